@@ -1,0 +1,550 @@
+// Fused Bloom-filtered beam search, one query per 128-thread block, persistent over the batch.
+//
+// What it computes is the traversal of the reference kernel
+// (src/search/topology_search_kernel.cu:2190-2664): same Bloom filter (hashes :382-385,611-653,
+// cleared and rebuilt from the top-L prefix on every third merge :2394-2411,2636-2654), same
+// candidate order (distance, raw id) (:414-420), same merge tie rule (:1338-1424), same selection
+// of the first W unexpanded ranks without a max_expansions re-check (:2479-2513), same ADC
+// summation tree (:656-692), same learned stop (:953-1137). Visited tests and adds of one batch
+// of slots run as two phases (all tests, barrier, all adds), which is the deterministic protocol
+// of the reference's micro-batch kernels (:2078-2106); the fused reference kernel leaves that
+// order to warp timing (:2556-2563).
+//
+// How it differs in construction: the query's look-up table lives in shared memory (built in
+// place from the query and the PQ pivots, or staged from HBM), the Bloom filter lives in shared
+// memory, every thread owns one frontier slot (its own 4-byte adjacency load, its own 16-byte
+// code loads, a register-resident tree sum), the frontier is sorted as 64-bit keys with warp
+// shuffles, and the merge is a parallel merge-path into a second buffer instead of a
+// single-thread backward merge.
+
+#include "beam_args.h"
+#include "tann_launch.h"
+
+namespace tann {
+
+constexpr int kBeamThreads = 128;
+
+// State written by thread 0 (or benignly by any thread) and read by the block after a barrier.
+// Counters every thread can derive identically (valid, visited, merges since the last Bloom
+// rebuild) are kept in registers instead.
+struct BeamCtl {
+    uint32_t expanded, iterations, first_full;
+    uint32_t nsel, stop;
+    uint32_t selected[TANN_MAX_SEARCH_WIDTH];
+    // learned stop state (:2252-2258)
+    uint32_t ls_stage, ls_has_prev, ls_topk_changed;
+    float ls_prev_dk, ls_prev_boundary;
+    uint32_t ls_prev_ids[32];
+};
+
+constexpr unsigned long long kInvalidKey = 0xff800000ffffffffull;  // KeyOf(+inf, 0xffffffff)
+
+__device__ __forceinline__ uint32_t CountBitsInRange(const uint32_t* bits, uint32_t b, uint32_t e) {
+    uint32_t n = 0;
+    for (uint32_t i = b; i < e; ++i) n += (bits[i >> 5] >> (i & 31)) & 1u;
+    return n;
+}
+__device__ __forceinline__ uint32_t FindFirstSetBit(const uint32_t* bits, uint32_t limit) {
+    const uint32_t words = (limit + 31) / 32;
+    for (uint32_t w = 0; w < words; ++w) {
+        uint32_t word = bits[w];
+        if (w + 1 == words && (limit & 31)) word &= (1u << (limit & 31)) - 1u;
+        if (word) return w * 32 + __ffs(word) - 1;
+    }
+    return limit;
+}
+
+// Learned stop on one thread; returns true when the traversal has to stop.
+__device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t valid, uint32_t visited,
+                            const Cand* cand, const uint32_t* unexp, uint32_t top_l) {
+    while (s.ls_stage < ls.num_stages) {
+        const uint32_t p = ls.stage_prefixes[s.ls_stage];
+        if (p == 0 || p >= top_l || p < ls.top_k) { ++s.ls_stage; continue; }
+        if (valid < top_l || valid < p || valid < ls.top_k || s.expanded < p) break;
+        const float dk = cand[ls.top_k - 1].dist;
+        const float boundary = cand[p - 1].dist;
+        const uint32_t next64_end = min(p + 64u, top_l);
+        const uint32_t next256_end = min(p + 256u, top_l);
+        const uint32_t next64_span = next64_end > p ? next64_end - p : 1u;
+        const uint32_t next256_span = next256_end > p ? next256_end - p : 1u;
+        const uint32_t gap32_index = min(max(ls.top_k - 1u, 31u), p - 1u);
+        const bool has_prev = s.ls_has_prev != 0;
+        float f[TANN_STOP_FEATURES];
+        f[0] = ls.feature_mask[0] ? (float)p * ls.inv_top_l : 0.0f;
+        f[1] = ls.feature_mask[1] ? (float)s.expanded * ls.inv_top_l : 0.0f;
+        f[2] = ls.feature_mask[2] ? (float)visited * ls.inv_top_l : 0.0f;
+        const bool need_best = ls.feature_mask[3] || (ls.feature_mask[4] && ls.next64_flag_mode);
+        uint32_t best = top_l;
+        if (need_best) {
+            best = FindFirstSetBit(unexp, top_l);
+            f[3] = ls.feature_mask[3] ? (float)best * ls.inv_top_l : 0.0f;
+        } else {
+            f[3] = 0.0f;
+        }
+        if (ls.feature_mask[4]) {
+            if (ls.next64_flag_mode) f[4] = best < next64_end ? 1.0f : 0.0f;
+            else f[4] = (float)CountBitsInRange(unexp, p, next64_end) / (float)next64_span;
+        } else {
+            f[4] = 0.0f;
+        }
+        f[5] = ls.feature_mask[5] ? (float)CountBitsInRange(unexp, p, next256_end) / (float)next256_span
+                                  : 0.0f;
+        f[6] = ls.feature_mask[6] ? dk : 0.0f;
+        f[7] = ls.feature_mask[7] ? (boundary - dk) : 0.0f;
+        f[8] = ls.feature_mask[8] ? (cand[gap32_index].dist - dk) : 0.0f;
+        f[9] = (ls.feature_mask[9] && has_prev) ? (s.ls_prev_dk - dk) : 0.0f;
+        f[10] = (ls.feature_mask[10] && has_prev) ? (s.ls_prev_boundary - boundary) : 0.0f;
+        if (!ls.feature_mask[11]) {
+            f[11] = 0.0f;
+        } else if (ls.topk_churn_flag_mode) {
+            f[11] = s.ls_topk_changed ? 1.0f : 0.0f;
+        } else if (!has_prev) {
+            f[11] = 1.0f;
+        } else {
+            uint32_t changed = 0;
+            for (uint32_t i = 0; i < ls.top_k; ++i) {
+                const uint32_t cur = RawId(cand[i].id);
+                bool found = false;
+                for (uint32_t j = 0; j < ls.top_k; ++j)
+                    if (s.ls_prev_ids[j] == cur) { found = true; break; }
+                changed += found ? 0u : 1u;
+            }
+            f[11] = (float)changed / (float)ls.top_k;
+        }
+        float logit = ls.bias;
+#pragma unroll
+        for (int i = 0; i < TANN_STOP_FEATURES; ++i) logit = fmaf(f[i], ls.weights[i], logit);
+        s.ls_prev_dk = dk;
+        s.ls_prev_boundary = boundary;
+        s.ls_has_prev = 1;
+        s.ls_topk_changed = 0;
+        if (ls.feature_mask[11] && !ls.topk_churn_flag_mode)
+            for (uint32_t i = 0; i < ls.top_k; ++i) s.ls_prev_ids[i] = RawId(cand[i].id);
+        if (logit < ls.threshold_logit) {
+            if (ls.shadow_mode) { s.ls_stage = ls.num_stages; break; }
+            return true;
+        }
+        ++s.ls_stage;
+    }
+    return false;
+}
+
+// ADC distance of one node by one thread, in the reference's order: per group of 32 chunks the
+// 16/8/4/2/1 tree over "lanes", groups added in order. Terms beyond M are exact zeros in the
+// reference and are simply left out here.
+template <int kM>
+__device__ __forceinline__ float AdcTreeThread(const float* lut, const uint8_t* row, uint32_t M) {
+    float total = 0.0f;
+    if constexpr (kM > 0) {
+        static_assert(kM % 16 == 0, "specialised chunk counts are multiples of 16");
+        uint32_t w[kM / 4];
+        const uint4* r4 = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+        for (int i = 0; i < kM / 16; ++i) {
+            const uint4 v = __ldg(r4 + i);
+            w[4 * i + 0] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int base = 0; base < kM; base += 32) {
+            constexpr int kDummy = 0; (void)kDummy;
+            const int n = (kM - base) < 32 ? (kM - base) : 32;
+            float x[32];
+#pragma unroll
+            for (int l = 0; l < 32; ++l) {
+                if (l < n) {
+                    const int c = base + l;
+                    const uint32_t code = (w[c >> 2] >> ((c & 3) * 8)) & 0xffu;
+                    x[l] = lut[c * kCentroids + code];
+                }
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int i = 0; i < off; ++i)
+                    if (i + off < n) x[i] = x[i] + x[i + off];
+            }
+            total = (base == 0) ? x[0] : total + x[0];
+        }
+    } else {
+        for (uint32_t base = 0; base < M; base += 32) {
+            const uint32_t n = min(32u, M - base);
+            float x[32];
+#pragma unroll
+            for (uint32_t l = 0; l < 32; ++l) {
+                x[l] = 0.0f;
+                if (l < n) x[l] = lut[(base + l) * kCentroids + __ldg(row + base + l)];
+            }
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int i = 0; i < off; ++i) x[i] = x[i] + x[i + off];
+            }
+            total = total + x[0];
+        }
+    }
+    return total;
+}
+
+// Bitonic sort of F keys held in shared memory (any power of two F).
+__device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
+    for (uint32_t k = 2; k <= F; k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t t = threadIdx.x; t < F / 2; t += kBeamThreads) {
+                const uint32_t lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const uint32_t hi = lo | j;
+                const bool asc = (lo & k) == 0;
+                const unsigned long long a = keys[lo], b = keys[hi];
+                if ((a > b) == asc) { keys[lo] = b; keys[hi] = a; }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Bitonic sort of up to 128 keys, one per thread: strides below 32 by shuffle, the three strides
+// of 32 and 64 through shared memory. Returns this thread's sorted key (rank = threadIdx.x).
+__device__ __forceinline__ unsigned long long SortKeys128(unsigned long long key,
+                                                          unsigned long long* scratch) {
+    const uint32_t t = threadIdx.x;
+#pragma unroll
+    for (uint32_t k = 2; k <= 128; k <<= 1) {
+#pragma unroll
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            unsigned long long other;
+            if (j >= 32) {
+                scratch[t] = key;
+                __syncthreads();
+                other = scratch[t ^ j];
+                __syncthreads();
+            } else {
+                other = __shfl_xor_sync(kFull, key, j);
+            }
+            const bool asc = (t & k) == 0;
+            const bool lower = (t & j) == 0;
+            const bool take_min = (asc == lower);
+            key = take_min ? (key < other ? key : other) : (key > other ? key : other);
+        }
+    }
+    return key;
+}
+
+// kSingle: W * degree <= 128, so every thread owns at most one frontier slot per batch and its
+// sort key never leaves registers until the merge.
+template <int kM, bool kSingle>
+__global__ void __launch_bounds__(kBeamThreads)
+beam_search_kernel(const __grid_constant__ BeamArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const uint32_t M = kM > 0 ? (uint32_t)kM : a.ix.num_chunks;
+    const uint32_t C = a.p.candidate_capacity;
+    const uint32_t F = a.frontier_capacity;
+    const uint32_t L = a.p.top_l;
+    const uint32_t W = a.p.search_width;
+    const uint32_t deg = a.ix.degree;
+    const uint32_t slots = W * deg;
+    const uint32_t UW = (L + 31) / 32;
+    const uint32_t d = a.ix.dim;
+    const uint64_t N = a.ix.num_nodes;
+    const uint32_t FK = kSingle ? (uint32_t)kBeamThreads : F;  // keys held in shared memory
+
+    float* lut = reinterpret_cast<float*>(smem_raw);
+    Cand* cand_a = reinterpret_cast<Cand*>(lut + (size_t)M * kCentroids);
+    Cand* cand_b = cand_a + C;
+    unsigned long long* fkey = reinterpret_cast<unsigned long long*>(cand_b + C);
+    uint32_t* bloom = reinterpret_cast<uint32_t*>(fkey + FK);
+    uint32_t* unexp = bloom + kBloomWords;
+    uint32_t* offs = unexp + UW;
+    float* sq = reinterpret_cast<float*>(offs + M + 1);
+
+    __shared__ BeamCtl ctl;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31;
+    const Cand inval{__int_as_float(0x7f800000), kInvalid};
+
+    for (uint64_t q = blockIdx.x; q < a.num_queries; q += gridDim.x) {
+        // ---- per-query set-up --------------------------------------------------------------
+        if (a.lut != nullptr) {
+            const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
+            float4* dst = reinterpret_cast<float4*>(lut);
+            for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
+        } else {
+            // src/search/pq_query_tables.cu:33-52, one table entry per thread per step
+            for (uint32_t i = tid; i < d; i += kBeamThreads)
+                sq[i] = LoadAsFloat<float>(a.queries, a.query_kind, q * d + i) - __ldg(a.ix.pq_centroid + i);
+            for (uint32_t i = tid; i <= M; i += kBeamThreads) offs[i] = __ldg(a.ix.pq_chunk_offsets + i);
+            __syncthreads();
+            for (uint32_t e = tid; e < M * kCentroids; e += kBeamThreads) {
+                const uint32_t m = e >> 8, c = e & 255u;
+                float acc = 0.0f;
+                for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
+                    const float diff = __ldg(a.ix.pq_tables_col_major + (size_t)dim * kCentroids + c) - sq[dim];
+                    acc = fmaf(diff, diff, acc);
+                }
+                lut[e] = acc;
+            }
+        }
+        for (uint32_t i = tid; i < C; i += kBeamThreads) { cand_a[i] = inval; cand_b[i] = inval; }
+        for (uint32_t i = tid; i < kBloomWords; i += kBeamThreads) bloom[i] = 0u;
+        for (uint32_t i = tid; i < UW; i += kBeamThreads) unexp[i] = 0u;
+        if (tid == 0) {
+            ctl.expanded = ctl.iterations = 0;
+            ctl.first_full = 0xffffffffu;
+            ctl.nsel = 0; ctl.stop = 0;
+            ctl.ls_stage = 0; ctl.ls_has_prev = 0; ctl.ls_topk_changed = 0;
+            ctl.ls_prev_dk = __int_as_float(0x7f800000);
+            ctl.ls_prev_boundary = __int_as_float(0x7f800000);
+        }
+        if (tid < 32) ctl.ls_prev_ids[tid] = kInvalid;
+        __syncthreads();
+
+        // block-uniform state, identical in every thread
+        uint32_t valid = 0, visited = 0, hash_iter = 0;
+        Cand* cur = cand_a;
+        Cand* nxt = cand_b;
+        const uint32_t entry_begin = a.entry_offsets[q];
+        const uint32_t num_entries = a.entry_offsets[q + 1] - entry_begin;
+        const uint32_t entry_batches = slots == 0 ? 0 : (num_entries + slots - 1) / slots;
+        uint32_t batch = 0;
+        bool in_entries = entry_batches > 0;
+
+        // ---- one pass per batch of slot ids: entry batches first, then expansions ----------
+        while (true) {
+            uint32_t nslots;
+            if (in_entries) {
+                nslots = slots;
+            } else {
+                // stop tests and selection on one thread (:2414-2513)
+                if (tid == 0) {
+                    uint32_t stop = 0, nsel = 0;
+                    if (ctl.expanded >= a.p.max_expansions || valid == 0) {
+                        stop = 1;
+                    } else if (a.p.learned_stop.enabled &&
+                               LearnedStop(a.p.learned_stop, ctl, valid, visited, cur, unexp, L)) {
+                        stop = 1;
+                    } else {
+                        const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
+                        bool any = false;
+                        if (prefix_stop && a.p.stop_use_expanded) {
+                            any = !(valid >= L && ctl.expanded >= a.p.stop_prefix);
+                        } else {
+                            const uint32_t words = (prefix_stop && valid >= a.p.stop_prefix)
+                                                       ? (a.p.stop_prefix + 31) / 32 : UW;
+                            for (uint32_t w = 0; w < words; ++w) any |= unexp[w] != 0u;
+                        }
+                        if (!any) {
+                            stop = 1;
+                        } else {
+                            ++ctl.iterations;
+                            for (uint32_t w = 0; w < UW && nsel < W; ++w) {
+                                uint32_t word = unexp[w];
+                                while (word != 0u && nsel < W) {
+                                    const uint32_t bit = __ffs(word) - 1;
+                                    const uint32_t idx = w * 32 + bit;
+                                    word &= word - 1u;
+                                    unexp[w] &= ~(1u << bit);
+                                    if (idx >= C || idx >= L || idx >= valid) continue;
+                                    const uint32_t pid = cur[idx].id;
+                                    if (pid == kInvalid || (pid & kExpandedBit)) continue;
+                                    cur[idx].id = pid | kExpandedBit;
+                                    ctl.selected[nsel++] = pid & kRawMask;
+                                    ++ctl.expanded;
+                                }
+                            }
+                            if (nsel == 0) stop = 1;
+                        }
+                    }
+                    ctl.stop = stop;
+                    ctl.nsel = nsel;
+                }
+                __syncthreads();
+                if (ctl.stop) break;
+                nslots = ctl.nsel * deg;
+            }
+
+            // ---- phase 1: gather slot ids, Bloom tests ----------------------------------------
+            unsigned long long my_key = kInvalidKey;  // kSingle: this thread's slot
+            if (!kSingle)
+                for (uint32_t i = tid; i < F; i += kBeamThreads) fkey[i] = kInvalidKey;
+            const uint32_t rounds = kSingle ? 1u : (nslots + kBeamThreads - 1) / kBeamThreads;
+            if (!kSingle) __syncthreads();
+            for (uint32_t r = 0; r < rounds; ++r) {
+                const uint32_t s = r * kBeamThreads + tid;
+                uint32_t id = kInvalid;
+                if (s < nslots) {
+                    if (in_entries) {
+                        const uint64_t e = (uint64_t)batch * slots + s;
+                        if (e < num_entries) id = __ldg(a.entry_ids + entry_begin + e);
+                    } else {
+                        const uint32_t k = s / deg, j = s - k * deg;
+                        const uint32_t node = ctl.selected[k];
+                        const uint32_t* row =
+                            (node < a.ix.adjacency_cached_rows)
+                                ? a.ix.adjacency_cache + (uint64_t)node * deg
+                                : reinterpret_cast<const uint32_t*>(
+                                      ShardRow(a.ix.adjacency, node, (uint64_t)deg * 4));
+                        id = __ldg(row + j);
+                    }
+                }
+                const bool pass = id != kInvalid && id < N && !BloomTest(id, bloom);
+                // Park the surviving id in the key slot; phase 2 turns it into a key.
+                const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
+                if (kSingle) my_key = parked; else if (s < F) fkey[s] = parked;
+            }
+            __syncthreads();  // every test of the batch precedes every add
+            // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
+            uint32_t fv = 0;
+            for (uint32_t r = 0; r < rounds; ++r) {
+                const uint32_t s = r * kBeamThreads + tid;
+                const unsigned long long parked = kSingle ? my_key : (s < F ? fkey[s] : kInvalidKey);
+                const bool pass = parked != kInvalidKey;
+                if (pass) {
+                    const uint32_t id = (uint32_t)parked;
+                    BloomAdd(id, bloom);
+                    const uint8_t* row = ShardRow(a.ix.codes, id, M);
+                    const float dist = AdcTreeThread<kM>(lut, row, M);
+                    const unsigned long long key = KeyOf(dist, id);
+                    if (kSingle) my_key = key; else fkey[s] = key;
+                }
+                fv += __syncthreads_count(pass);
+            }
+
+            // ---- sort the frontier ---------------------------------------------------------------
+            if (kSingle) {
+                my_key = SortKeys128(my_key, fkey);
+                fkey[tid] = my_key;  // rank = thread index; invalid keys sort last
+                __syncthreads();
+            } else {
+                SortKeysShared(fkey, F);
+            }
+
+            // ---- merge (:1338-1424) as a parallel merge-path --------------------------------------
+            const uint32_t nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
+            uint32_t accepted = 0;
+            {
+                const uint32_t lim = min(fv, nv);
+                for (uint32_t base = 0; base < lim; base += kBeamThreads) {
+                    const uint32_t x = base + tid;
+                    bool pred = false;
+                    if (x < lim) pred = fkey[x] < KeyOf(cur[nv - 1 - x]);
+                    const uint32_t cnt = __syncthreads_count(pred);
+                    accepted += cnt;
+                    if (cnt < (uint32_t)kBeamThreads) break;  // the predicate is monotone in x
+                }
+            }
+            if (accepted != 0) {
+                const uint32_t kept = nv - accepted;
+                for (uint32_t i = tid; i < kept; i += kBeamThreads) {
+                    const Cand c = cur[i];
+                    const unsigned long long ck = KeyOf(c);
+                    uint32_t lo = 0, hi = accepted;  // frontier keys <= ck go in front of it
+                    while (lo < hi) {
+                        const uint32_t mid = (lo + hi) >> 1;
+                        if (fkey[mid] <= ck) lo = mid + 1; else hi = mid;
+                    }
+                    nxt[i + lo] = c;
+                }
+                bool changed = false;
+                for (uint32_t j = tid; j < accepted; j += kBeamThreads) {
+                    const unsigned long long fk = fkey[j];
+                    uint32_t lo = 0, hi = kept;  // kept candidates < fk stay in front of it
+                    while (lo < hi) {
+                        const uint32_t mid = (lo + hi) >> 1;
+                        if (KeyOf(cur[mid]) < fk) lo = mid + 1; else hi = mid;
+                    }
+                    Cand c;
+                    c.dist = FromOrderedBits((uint32_t)(fk >> 32));
+                    c.id = (uint32_t)fk;
+                    nxt[j + lo] = c;
+                    changed |= (j + lo) < a.p.learned_stop.top_k;
+                }
+                for (uint32_t i = nv + tid; i < C; i += kBeamThreads) nxt[i] = inval;
+                if (changed) ctl.ls_topk_changed = 1;
+                Cand* t = cur; cur = nxt; nxt = t;
+            }
+            valid = nv;
+            visited += fv;
+            ++hash_iter;
+            const bool rebuild = hash_iter >= 3;
+            if (rebuild) {
+                hash_iter = 0;
+                for (uint32_t i = tid; i < kBloomWords; i += kBeamThreads) bloom[i] = 0u;
+            }
+            if (tid == 0 && ctl.first_full == 0xffffffffu && nv >= L)
+                ctl.first_full = in_entries ? 0u : ctl.iterations;
+            __syncthreads();
+            // ---- prefix state (:822-845): unexpanded bitmap, Bloom rebuild every third merge ----
+            const uint32_t prefix = min(nv, L);
+            for (uint32_t base = 0; base < UW * 32; base += kBeamThreads) {
+                const uint32_t i = base + tid;
+                bool un = false;
+                if (i < prefix) {
+                    const uint32_t pid = cur[i].id;
+                    if (pid != kInvalid) {
+                        un = (pid & kExpandedBit) == 0;
+                        if (rebuild) BloomAdd(pid & kRawMask, bloom);
+                    }
+                }
+                const uint32_t word = __ballot_sync(kFull, un);
+                if (lane == 0 && (i >> 5) < UW) unexp[i >> 5] = word;
+            }
+            __syncthreads();
+
+            if (in_entries) {
+                ++batch;
+                if (batch >= entry_batches) in_entries = false;
+            }
+        }
+
+        // ---- results -----------------------------------------------------------------------------
+        Cand* out = a.out_cand + q * (uint64_t)C;
+        for (uint32_t i = tid; i < C; i += kBeamThreads) out[i] = cur[i];
+        if (tid == 0) {
+            uint32_t* st = a.out_stats + q * 8;
+            st[0] = visited; st[1] = ctl.expanded; st[2] = 0; st[3] = ctl.iterations;
+            st[4] = valid; st[5] = ctl.first_full; st[6] = 0; st[7] = 0;
+        }
+        __syncthreads();
+    }
+}
+
+size_t BeamSmemBytes(uint32_t M, uint32_t C, uint32_t F, uint32_t L, uint32_t d) {
+    const size_t uw = (L + 31) / 32;
+    const size_t fk = F <= (uint32_t)kBeamThreads ? (size_t)kBeamThreads : F;
+    size_t bytes = (size_t)M * kCentroids * 4 + (size_t)2 * C * 8 + fk * 8 + kBloomWords * 4 +
+                   uw * 4 + ((size_t)M + 1) * 4 + (size_t)d * 4;
+    return (bytes + 15) & ~(size_t)15;
+}
+
+typedef void (*BeamKernel)(const BeamArgs);
+
+template <bool kSingle>
+static BeamKernel PickByChunks(uint32_t M) {
+    switch (M) {
+        case 16: return beam_search_kernel<16, kSingle>;
+        case 32: return beam_search_kernel<32, kSingle>;
+        case 48: return beam_search_kernel<48, kSingle>;
+        case 64: return beam_search_kernel<64, kSingle>;
+        case 96: return beam_search_kernel<96, kSingle>;
+        default: return beam_search_kernel<0, kSingle>;
+    }
+}
+
+BeamKernel PickBeamKernel(uint32_t M, uint32_t slots) {
+    return slots <= (uint32_t)kBeamThreads ? PickByChunks<true>(M) : PickByChunks<false>(M);
+}
+
+cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream_t stream) {
+    BeamKernel k = PickBeamKernel(a.ix.num_chunks, a.p.search_width * a.ix.degree);
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    k<<<grid, kBeamThreads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
+cudaError_t BeamOccupancy(uint32_t M, uint32_t slots, size_t smem, int* blocks_per_sm) {
+    BeamKernel k = PickBeamKernel(M, slots);
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, k, kBeamThreads, smem);
+}
+
+}  // namespace tann

@@ -1,0 +1,589 @@
+// C ABI of the library: argument checks, launches, and the searcher that chains the whole path.
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "beam_args.h"
+#include "tann_launch.h"
+#include "topoanns_b200.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+TannStatus Fail(TannStatus st, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return st;
+}
+
+TannStatus CudaFail(cudaError_t e, const char* what) {
+    return Fail(TANN_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+#define TANN_CUDA(call)                                   \
+    do {                                                  \
+        cudaError_t e__ = (call);                         \
+        if (e__ != cudaSuccess) return CudaFail(e__, #call); \
+    } while (0)
+
+uint32_t NextPow2(uint32_t v) {
+    uint32_t p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+TannStatus CheckShards(const TannShards& s, uint64_t rows, const char* name) {
+    if (s.num_shards == 0 || s.num_shards > TANN_MAX_SHARDS)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: num_shards must be 1..%d.", name, TANN_MAX_SHARDS);
+    for (uint32_t i = 0; i < s.num_shards; ++i)
+        if (s.base[i] == nullptr) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: shard %u has no base pointer.", name, i);
+    if (s.num_shards > 1 && (s.rows_per_shard == 0 || s.rows_per_shard * s.num_shards < rows))
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: shards do not cover all rows.", name);
+    return TANN_OK;
+}
+
+// Parameter rules of the reference: src/search/topology_search.cpp:16-35,
+// src/search/topology_search_kernel.cu:3193-3206.
+TannStatus CheckBeam(const TannIndexView* ix, const TannBeamParams* p) {
+    if (ix == nullptr || p == nullptr) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: null index or params.");
+    if (p->top_l == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: top_l must be positive.");
+    if (p->search_width == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: search_width must be positive.");
+    if (p->search_width > TANN_MAX_SEARCH_WIDTH)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: search_width must be at most 32.");
+    if (p->max_expansions == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: max_expansions must be positive.");
+    if (ix->num_nodes >= 0x7fffffffull)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: packed node_id requires num_nodes < 2^31 - 1.");
+    if (p->candidate_capacity < p->top_l || (p->candidate_capacity & (p->candidate_capacity - 1)) != 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: candidate_capacity must be a power of two >= top_l.");
+    if (ix->degree == 0 || ix->num_chunks == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: degree and num_chunks must be positive.");
+    if ((uint64_t)p->search_width * ix->degree > 2048)
+        return Fail(TANN_ERR_UNSUPPORTED, "tann_beam_search: search_width * degree must be at most 2048.");
+    if (p->learned_stop.enabled && (p->learned_stop.top_k == 0 || p->learned_stop.top_k > 32 ||
+                                    p->learned_stop.num_stages > TANN_MAX_STOP_STAGES))
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: learned stop needs 1 <= top_k <= 32 and at most 32 stages.");
+    TannStatus st = CheckShards(ix->adjacency, ix->num_nodes, "adjacency");
+    if (st != TANN_OK) return st;
+    return CheckShards(ix->codes, ix->num_nodes, "codes");
+}
+
+struct BeamPlan {
+    uint32_t F;
+    size_t smem;
+    int blocks_per_sm;
+    uint32_t grid;
+};
+
+TannStatus PlanBeam(const TannIndexView* ix, const TannBeamParams* p, bool lut_in_kernel, uint64_t Q,
+                    BeamPlan* plan) {
+    (void)lut_in_kernel;
+    const uint32_t slots = p->search_width * ix->degree;
+    plan->F = NextPow2(slots == 0 ? 1 : slots);
+    plan->smem = tann::BeamSmemBytes(ix->num_chunks, p->candidate_capacity, plan->F, p->top_l, ix->dim);
+    int dev = 0, max_optin = 0;
+    TANN_CUDA(cudaGetDevice(&dev));
+    TANN_CUDA(cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (plan->smem > (size_t)max_optin)
+        return Fail(TANN_ERR_UNSUPPORTED,
+                    "tann_beam_search: shared memory requirement (%zu bytes) is too large for this device (%d).",
+                    plan->smem, max_optin);
+    TANN_CUDA(tann::BeamOccupancy(ix->num_chunks, slots, plan->smem, &plan->blocks_per_sm));
+    if (plan->blocks_per_sm < 1) plan->blocks_per_sm = 1;
+    const uint64_t resident = (uint64_t)tann::SmCount() * plan->blocks_per_sm;
+    plan->grid = (uint32_t)(Q < resident ? (Q == 0 ? 1 : Q) : resident);
+    return TANN_OK;
+}
+
+}  // namespace
+
+namespace tann {
+int SmCount() {
+    static thread_local int cached_dev = -1, cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+}  // namespace tann
+
+extern "C" {
+
+const char* tann_version(void) { return "topoanns_b200 0.1 (sm_100a)"; }
+const char* tann_last_error(void) { return g_error; }
+
+TannStatus tann_lut_build(const float* tables_col_major, const float* centroid,
+                          const uint32_t* chunk_offsets, uint32_t dim, uint32_t num_chunks,
+                          const void* queries, uint32_t query_kind, uint64_t num_queries,
+                          float* out_tables, tann_stream_t stream) {
+    if (dim == 0 || num_chunks == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_lut_build: PQ index is empty.");
+    if (query_kind > TANN_KIND_FLOAT32) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_lut_build: unknown query kind.");
+    if (num_queries == 0) return TANN_OK;
+    if (!tables_col_major || !centroid || !chunk_offsets || !queries || !out_tables)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_lut_build: null pointer.");
+    TANN_CUDA(tann::LaunchLutBuild(tables_col_major, centroid, chunk_offsets, dim, num_chunks, queries,
+                                   query_kind, num_queries, out_tables, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_beam_search(const TannIndexView* index, const TannBeamParams* params, const float* lut,
+                            const void* queries, uint32_t query_kind, uint64_t num_queries,
+                            const uint32_t* entry_offsets, const uint32_t* entry_ids,
+                            void* out_candidates, uint32_t* out_stats, uint32_t* status,
+                            tann_stream_t stream) {
+    TannStatus st = CheckBeam(index, params);
+    if (st != TANN_OK) return st;
+    if (num_queries == 0) return TANN_OK;
+    if (lut == nullptr) {
+        if (queries == nullptr || query_kind > TANN_KIND_FLOAT32)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: queries are needed when no table is given.");
+        if (!index->pq_tables_col_major || !index->pq_centroid || !index->pq_chunk_offsets)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: PQ index must be loaded before search.");
+    }
+    if (!entry_offsets || !entry_ids || !out_candidates || !out_stats)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: null pointer.");
+    BeamPlan plan;
+    st = PlanBeam(index, params, lut == nullptr, num_queries, &plan);
+    if (st != TANN_OK) return st;
+    tann::BeamArgs a;
+    memset(&a, 0, sizeof(a));
+    a.ix = *index;
+    a.p = *params;
+    a.lut = lut;
+    a.queries = queries;
+    a.query_kind = query_kind;
+    a.frontier_capacity = plan.F;
+    a.num_queries = num_queries;
+    a.entry_offsets = entry_offsets;
+    a.entry_ids = entry_ids;
+    a.out_cand = static_cast<tann::Cand*>(out_candidates);
+    a.out_stats = out_stats;
+    a.status = status;
+    TANN_CUDA(tann::LaunchBeam(a, plan.smem, plan.grid, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_beam_search_occupancy(const TannIndexView* index, const TannBeamParams* params,
+                                      int lut_in_kernel, uint32_t* smem_bytes, uint32_t* blocks_per_sm,
+                                      uint32_t* grid_blocks) {
+    TannStatus st = CheckBeam(index, params);
+    if (st != TANN_OK) return st;
+    BeamPlan plan;
+    st = PlanBeam(index, params, lut_in_kernel != 0, ~0ull, &plan);
+    if (st != TANN_OK) return st;
+    if (smem_bytes) *smem_bytes = (uint32_t)plan.smem;
+    if (blocks_per_sm) *blocks_per_sm = (uint32_t)plan.blocks_per_sm;
+    if (grid_blocks) *grid_blocks = plan.grid;
+    return TANN_OK;
+}
+
+TannStatus tann_rvq_norms(const float* rows, uint32_t count, uint32_t dim, float* out_norms,
+                          tann_stream_t stream) {
+    if (count == 0) return TANN_OK;
+    if (!rows || !out_norms || dim == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rvq_norms: null pointer or zero dim.");
+    TANN_CUDA(tann::LaunchRvqNorms(rows, count, dim, out_norms, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_rvq_entries(const float* queries, uint64_t num_queries, uint32_t dim, const float* coarse,
+                            const float* coarse_t, const float* coarse_norms, uint32_t num_coarse,
+                            const float* fine_t, const float* fine_norms, uint32_t num_fine,
+                            const int32_t* bucket_sizes, const uint32_t* cluster_offsets,
+                            const uint32_t* cluster_ids, uint32_t entry_count, uint32_t fallback_entry,
+                            int32_t* out_clusters, uint32_t* out_entry_ids, uint32_t* out_entry_offsets,
+                            tann_stream_t stream) {
+    if (entry_count == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rvq_entries: entry_count must be positive.");
+    if (num_queries == 0) return TANN_OK;
+    if (!queries || !coarse || !coarse_t || !coarse_norms || !fine_t || !fine_norms || !bucket_sizes ||
+        !cluster_offsets || !cluster_ids || !out_entry_ids || dim == 0 || num_coarse == 0 || num_fine == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rvq_entries: model is not loaded.");
+    if (num_queries * entry_count > 0xffffffffull)
+        return Fail(TANN_ERR_UNSUPPORTED, "tann_rvq_entries: entry offsets overflow uint32.");
+    TANN_CUDA(tann::LaunchRvqEntries(queries, num_queries, dim, coarse, coarse_t, coarse_norms, num_coarse,
+                                     fine_t, fine_norms, num_fine, bucket_sizes, cluster_offsets,
+                                     cluster_ids, entry_count, fallback_entry, out_clusters, out_entry_ids,
+                                     out_entry_offsets, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_pq2_refine(const void* candidates, const uint32_t* stats, uint64_t num_queries,
+                           uint32_t capacity, uint32_t refine_top_l, const TannShards* base_codes,
+                           const TannShards* pq2_codes, uint32_t num_chunks, const float* lut2,
+                           const float* cross_terms, void* out_candidates, uint32_t* status,
+                           tann_stream_t stream) {
+    (void)status;
+    if (num_queries == 0 || refine_top_l == 0) return TANN_OK;
+    if (!candidates || !stats || !pq2_codes || !lut2 || !out_candidates)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_pq2_refine: PQ2 index must be loaded.");
+    // src/search/rerank_exact.cu:2285-2296
+    if (num_chunks > 256) return Fail(TANN_ERR_UNSUPPORTED, "tann_pq2_refine: PQ2 num_chunks exceeds kernel specialization limit.");
+    if (refine_top_l > capacity) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_pq2_refine: refine_top_l exceeds topology candidate capacity.");
+    if (refine_top_l > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_pq2_refine: refine_top_l exceeds device bitonic sort limit.");
+    if (base_codes != nullptr && cross_terms == nullptr)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_pq2_refine: residual refine needs cross terms.");
+    TANN_CUDA(tann::LaunchPq2Refine(candidates, stats, num_queries, capacity, refine_top_l, base_codes,
+                                    *pq2_codes, num_chunks, lut2, cross_terms, out_candidates,
+                                    (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks, const uint32_t* chunk_offsets,
+                                const float* tables1_row_major, const float* centroid1,
+                                const float* tables2_row_major, const float* centroid2, float* out,
+                                tann_stream_t stream) {
+    if (!chunk_offsets || !tables1_row_major || !centroid1 || !tables2_row_major || !centroid2 || !out)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_pq2_cross_terms: null pointer.");
+    TANN_CUDA(tann::LaunchCrossTerms(dim, num_chunks, chunk_offsets, tables1_row_major, centroid1,
+                                     tables2_row_major, centroid2, out, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams* params,
+                             const void* candidates, uint32_t capacity, uint64_t num_queries,
+                             const void* queries, uint32_t query_kind, const float* error_bounds,
+                             float* out_dists, uint32_t* out_ids, unsigned long long* out_counts,
+                             uint32_t* status, tann_stream_t stream) {
+    (void)status;
+    if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null index or params.");
+    if (num_queries == 0 || params->top_n == 0) return TANN_OK;
+    if (index->vectors.base[0] == nullptr || index->vector_bytes == 0 || index->vectors_per_page == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: Vector store must be loaded before rerank.");
+    if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null pointer.");
+    if (params->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
+    if (params->use_bound_filter) {  // src/search/rerank_exact.cu:2564-2585
+        if (params->top_k == 0 || params->top_k > 128)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires 1 <= top_k <= 128.");
+        if (error_bounds == nullptr)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires residual PQ2 error bounds.");
+    }
+    TannStatus st = CheckShards(index->vectors, index->num_nodes, "vectors");
+    if (st != TANN_OK) return st;
+    TANN_CUDA(tann::LaunchRerank(*index, *params, candidates, capacity, num_queries, queries, query_kind,
+                                 error_bounds, out_dists, out_ids, out_counts, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+TannStatus tann_topk_pack(const float* dists, const uint32_t* ids, uint64_t num_queries, uint32_t top_n,
+                          uint32_t top_k, float* out_dists, uint32_t* out_ids, tann_stream_t stream) {
+    if (num_queries == 0 || top_k == 0) return TANN_OK;
+    if (!dists || !ids || !out_dists || !out_ids) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_topk_pack: null pointer.");
+    TANN_CUDA(tann::LaunchTopkPack(dists, ids, num_queries, top_n, top_k, out_dists, out_ids, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+// ---- memory helpers ---------------------------------------------------------------------------
+
+TannStatus tann_device_alloc(uint64_t bytes, void** out_dev) {
+    if (!out_dev) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_device_alloc: null out pointer.");
+    *out_dev = nullptr;
+    if (bytes == 0) return TANN_OK;
+    TANN_CUDA(cudaMalloc(out_dev, bytes));
+    return TANN_OK;
+}
+TannStatus tann_device_free(void* dev) {
+    if (dev) TANN_CUDA(cudaFree(dev));
+    return TANN_OK;
+}
+TannStatus tann_host_alloc_mapped(uint64_t bytes, void** out_host, void** out_dev) {
+    if (!out_host || !out_dev) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_host_alloc_mapped: null out pointer.");
+    *out_host = *out_dev = nullptr;
+    if (bytes == 0) return TANN_OK;
+    TANN_CUDA(cudaHostAlloc(out_host, bytes, cudaHostAllocMapped | cudaHostAllocPortable));
+    cudaError_t e = cudaHostGetDevicePointer(out_dev, *out_host, 0);
+    if (e != cudaSuccess) {
+        cudaFreeHost(*out_host);
+        *out_host = nullptr;
+        return CudaFail(e, "cudaHostGetDevicePointer");
+    }
+    return TANN_OK;
+}
+TannStatus tann_host_free(void* host) {
+    if (host) TANN_CUDA(cudaFreeHost(host));
+    return TANN_OK;
+}
+TannStatus tann_ipc_export(void* dev, unsigned char handle[TANN_IPC_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) <= TANN_IPC_HANDLE_BYTES, "handle size");
+    if (!dev || !handle) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_ipc_export: null pointer.");
+    cudaIpcMemHandle_t h;
+    TANN_CUDA(cudaIpcGetMemHandle(&h, dev));
+    memset(handle, 0, TANN_IPC_HANDLE_BYTES);
+    memcpy(handle, &h, sizeof(h));
+    return TANN_OK;
+}
+TannStatus tann_ipc_open(const unsigned char handle[TANN_IPC_HANDLE_BYTES], void** out_dev) {
+    if (!handle || !out_dev) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_ipc_open: null pointer.");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    TANN_CUDA(cudaIpcOpenMemHandle(out_dev, h, cudaIpcMemLazyEnablePeerAccess));
+    return TANN_OK;
+}
+TannStatus tann_ipc_close(void* dev) {
+    if (dev) TANN_CUDA(cudaIpcCloseMemHandle(dev));
+    return TANN_OK;
+}
+TannStatus tann_enable_peer_access(int peer_device) {
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();
+        return TANN_OK;
+    }
+    if (e != cudaSuccess) return CudaFail(e, "cudaDeviceEnablePeerAccess");
+    return TANN_OK;
+}
+
+// ---- searcher -----------------------------------------------------------------------------------
+
+struct TannSearcher {
+    TannIndexView ix;
+    uint64_t max_queries;
+    uint32_t max_capacity, max_top_n, max_entries;
+    bool has_rvq, has_pq2;
+    TannRvqModelView rvq;
+    TannPq2View pq2;
+    // device work space
+    void* d_queries;          // max_queries * dim * 4
+    float* d_queries_f32;     // float copy of the queries for RVQ / pq2 when the kind is not float
+    uint32_t* d_entry_offsets;
+    uint32_t* d_entry_ids;
+    void* d_cand;
+    void* d_cand_refined;
+    uint32_t* d_stats;
+    float* d_lut2;
+    float* d_dists;
+    uint32_t* d_ids;
+    float* d_topk_dists;
+    uint32_t* d_topk_ids;
+    unsigned long long* d_counts;
+    // pinned staging
+    void* h_queries;
+    uint32_t* h_topk_ids;
+    float* h_topk_dists;
+    uint32_t* h_stats;
+    uint32_t* h_entries;
+};
+
+static void FreeSearcher(TannSearcher* s) {
+    if (!s) return;
+    cudaFree(s->d_queries); cudaFree(s->d_queries_f32); cudaFree(s->d_entry_offsets);
+    cudaFree(s->d_entry_ids); cudaFree(s->d_cand); cudaFree(s->d_cand_refined); cudaFree(s->d_stats);
+    cudaFree(s->d_lut2); cudaFree(s->d_dists); cudaFree(s->d_ids); cudaFree(s->d_topk_dists);
+    cudaFree(s->d_topk_ids); cudaFree(s->d_counts);
+    cudaFreeHost(s->h_queries); cudaFreeHost(s->h_topk_ids); cudaFreeHost(s->h_topk_dists);
+    cudaFreeHost(s->h_stats); cudaFreeHost(s->h_entries);
+    cudaGetLastError();
+    delete s;
+}
+
+TannStatus tann_searcher_create(const TannIndexView* index, uint64_t max_queries,
+                                uint32_t max_candidate_capacity, uint32_t max_top_n,
+                                uint32_t max_entries_per_query, TannSearcher** out) {
+    if (!index || !out) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_create: null pointer.");
+    *out = nullptr;
+    if (max_queries == 0 || max_candidate_capacity == 0 || max_top_n == 0 || max_entries_per_query == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_create: sizes must be positive.");
+    if (max_queries * max_entries_per_query > 0xffffffffull)
+        return Fail(TANN_ERR_UNSUPPORTED, "tann_searcher_create: entry offsets overflow uint32.");
+    TannSearcher* s = new (std::nothrow) TannSearcher();
+    if (!s) return Fail(TANN_ERR_CUDA, "tann_searcher_create: out of host memory.");
+    memset(s, 0, sizeof(*s));
+    s->ix = *index;
+    s->max_queries = max_queries;
+    s->max_capacity = NextPow2(max_candidate_capacity);
+    s->max_top_n = max_top_n;
+    s->max_entries = max_entries_per_query;
+    const size_t Q = max_queries, d = index->dim;
+    cudaError_t e = cudaSuccess;
+    auto dev = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes ? bytes : 16); };
+    auto host = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaHostAlloc(p, bytes ? bytes : 16, cudaHostAllocDefault); };
+    dev(&s->d_queries, Q * d * 4);
+    dev((void**)&s->d_queries_f32, Q * d * 4);
+    dev((void**)&s->d_entry_offsets, (Q + 1) * 4);
+    dev((void**)&s->d_entry_ids, Q * max_entries_per_query * 4);
+    dev(&s->d_cand, Q * s->max_capacity * 8);
+    dev(&s->d_cand_refined, Q * s->max_capacity * 8);
+    dev((void**)&s->d_stats, Q * 8 * 4);
+    dev((void**)&s->d_dists, Q * max_top_n * 4);
+    dev((void**)&s->d_ids, Q * max_top_n * 4);
+    dev((void**)&s->d_topk_dists, Q * max_top_n * 4);
+    dev((void**)&s->d_topk_ids, Q * max_top_n * 4);
+    dev((void**)&s->d_counts, 16);
+    host(&s->h_queries, Q * d * 4);
+    host((void**)&s->h_topk_ids, Q * max_top_n * 4);
+    host((void**)&s->h_topk_dists, Q * max_top_n * 4);
+    host((void**)&s->h_stats, Q * 8 * 4);
+    host((void**)&s->h_entries, (size_t)max_entries_per_query * 4);
+    if (e != cudaSuccess) {
+        FreeSearcher(s);
+        return CudaFail(e, "tann_searcher_create");
+    }
+    *out = s;
+    return TANN_OK;
+}
+
+TannStatus tann_searcher_set_rvq(TannSearcher* s, const TannRvqModelView* rvq) {
+    if (!s) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_rvq: null searcher.");
+    if (!rvq) { s->has_rvq = false; return TANN_OK; }
+    if (rvq->dim != s->ix.dim) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_rvq: model dim differs from the index dim.");
+    if (rvq->entry_count == 0 || rvq->entry_count > s->max_entries)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_rvq: entry_count must be 1..max_entries_per_query.");
+    s->rvq = *rvq;
+    s->has_rvq = true;
+    return TANN_OK;
+}
+
+TannStatus tann_searcher_set_pq2(TannSearcher* s, const TannPq2View* pq2) {
+    if (!s) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_pq2: null searcher.");
+    if (!pq2 || !pq2->enabled) { s->has_pq2 = false; return TANN_OK; }
+    if (s->d_lut2 == nullptr) {
+        TANN_CUDA(cudaMalloc((void**)&s->d_lut2, s->max_queries * (size_t)s->ix.num_chunks * 256 * 4));
+    }
+    s->pq2 = *pq2;
+    s->has_pq2 = true;
+    return TANN_OK;
+}
+
+__global__ void to_float_kernel(const void* src, uint32_t kind, uint64_t n, float* dst) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+        dst[i] = kind == TANN_KIND_UINT8 ? (float)static_cast<const uint8_t*>(src)[i]
+                                          : (float)static_cast<const int8_t*>(src)[i];
+}
+__global__ void fixed_entries_kernel(const uint32_t* entries, uint32_t n, uint64_t Q, uint32_t* offsets,
+                                     uint32_t* ids) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < Q * n; i += (uint64_t)gridDim.x * blockDim.x)
+        ids[i] = entries[i % n];
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= Q; i += (uint64_t)gridDim.x * blockDim.x)
+        offsets[i] = (uint32_t)(i * n);
+}
+
+TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
+                                    const TannRerankParams* rerank, const void* queries_dev,
+                                    uint32_t query_kind, uint64_t Q, const uint32_t* entry_offsets_dev,
+                                    const uint32_t* entry_ids_dev, const uint32_t** out_ids_dev,
+                                    const float** out_dists_dev, const uint32_t** out_stats_dev,
+                                    tann_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!s || !beam || !rerank) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: null pointer.");
+    if (Q > s->max_queries) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: batch exceeds max_queries.");
+    if (beam->candidate_capacity > s->max_capacity) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: candidate capacity exceeds the searcher's.");
+    if (rerank->top_n > s->max_top_n || rerank->top_k > rerank->top_n)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: need top_k <= top_n <= max_top_n.");
+    if (rerank->top_n > beam->candidate_capacity)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: top_n exceeds the candidate capacity.");
+    if (Q == 0) return TANN_OK;
+    const uint32_t d = s->ix.dim;
+    const float* qf32 = static_cast<const float*>(queries_dev);
+    const bool need_f32 = (s->has_rvq && entry_offsets_dev == nullptr) || s->has_pq2;
+    if (query_kind != TANN_KIND_FLOAT32 && need_f32) {
+        to_float_kernel<<<tann::SmCount() * 4, 256, 0, stream>>>(queries_dev, query_kind, Q * d, s->d_queries_f32);
+        TANN_CUDA(cudaGetLastError());
+        qf32 = s->d_queries_f32;
+    }
+    // entries
+    const uint32_t* eo = entry_offsets_dev;
+    const uint32_t* ei = entry_ids_dev;
+    if (eo == nullptr) {
+        if (!s->has_rvq) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: no entries and no RVQ model.");
+        const TannRvqModelView& r = s->rvq;
+        TannStatus st = tann_rvq_entries(qf32, Q, d, r.coarse, r.coarse_t, r.coarse_norms, r.num_coarse,
+                                         r.fine_t, r.fine_norms, r.num_fine, r.bucket_sizes,
+                                         r.cluster_offsets, r.cluster_ids, r.entry_count, r.fallback_entry,
+                                         nullptr, s->d_entry_ids, s->d_entry_offsets, stream);
+        if (st != TANN_OK) return st;
+        eo = s->d_entry_offsets;
+        ei = s->d_entry_ids;
+    }
+    // traversal, table built in the kernel
+    TannStatus st = tann_beam_search(&s->ix, beam, nullptr, queries_dev, query_kind, Q, eo, ei, s->d_cand,
+                                     s->d_stats, nullptr, stream);
+    if (st != TANN_OK) return st;
+    const void* cand = s->d_cand;
+    uint32_t capacity = beam->candidate_capacity;
+    const float* err = nullptr;
+    if (s->has_pq2) {
+        const TannPq2View& p2 = s->pq2;
+        // src/search/rerank_exact.cu:2610-2615
+        const uint32_t lr = p2.refine_top_l == 0 ? capacity : (p2.refine_top_l < capacity ? p2.refine_top_l : capacity);
+        st = tann_lut_build(p2.tables_col_major, p2.centroid, p2.chunk_offsets, d, s->ix.num_chunks, qf32,
+                            TANN_KIND_FLOAT32, Q, s->d_lut2, stream);
+        if (st != TANN_OK) return st;
+        st = tann_pq2_refine(s->d_cand, s->d_stats, Q, capacity, lr, p2.residual ? &s->ix.codes : nullptr,
+                             &p2.codes, s->ix.num_chunks, s->d_lut2, p2.cross_terms, s->d_cand_refined,
+                             nullptr, stream);
+        if (st != TANN_OK) return st;
+        cand = s->d_cand_refined;
+        capacity = lr;
+        err = p2.error_bounds;
+    }
+    st = tann_rerank_exact(&s->ix, rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
+                           s->d_ids, nullptr, nullptr, stream);
+    if (st != TANN_OK) return st;
+    st = tann_topk_pack(s->d_dists, s->d_ids, Q, rerank->top_n, rerank->top_k, s->d_topk_dists,
+                        s->d_topk_ids, stream);
+    if (st != TANN_OK) return st;
+    if (out_ids_dev) *out_ids_dev = s->d_topk_ids;
+    if (out_dists_dev) *out_dists_dev = s->d_topk_dists;
+    if (out_stats_dev) *out_stats_dev = s->d_stats;
+    return TANN_OK;
+}
+
+TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const TannRerankParams* rerank,
+                             const void* queries_host, uint32_t query_kind, uint64_t Q,
+                             const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
+                             uint32_t* out_ids_host, float* out_dists_host, uint32_t* out_stats_host,
+                             tann_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!s || !beam || !rerank || !queries_host || !out_ids_host || !out_dists_host)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: null pointer.");
+    if (Q > s->max_queries) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: batch exceeds max_queries.");
+    if (query_kind > TANN_KIND_FLOAT32) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: unknown query kind.");
+    if (Q == 0) return TANN_OK;
+    const size_t qbytes = Q * (size_t)s->ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
+    // One pinned staging copy keeps the H2D asynchronous whatever memory the caller hands in.
+    memcpy(s->h_queries, queries_host, qbytes);
+    TANN_CUDA(cudaMemcpyAsync(s->d_queries, s->h_queries, qbytes, cudaMemcpyHostToDevice, stream));
+    const uint32_t* eo = nullptr;
+    const uint32_t* ei = nullptr;
+    if (fixed_entries_host != nullptr && num_fixed_entries != 0) {
+        if (num_fixed_entries > s->max_entries)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: too many fixed entries.");
+        memcpy(s->h_entries, fixed_entries_host, (size_t)num_fixed_entries * 4);
+        // stage the list behind the per-query id array, then expand it on the device
+        uint32_t* d_list = reinterpret_cast<uint32_t*>(s->d_topk_ids);  // free until the last step
+        TANN_CUDA(cudaMemcpyAsync(d_list, s->h_entries, (size_t)num_fixed_entries * 4, cudaMemcpyHostToDevice, stream));
+        fixed_entries_kernel<<<tann::SmCount() * 2, 256, 0, stream>>>(d_list, num_fixed_entries, Q,
+                                                                      s->d_entry_offsets, s->d_entry_ids);
+        TANN_CUDA(cudaGetLastError());
+        eo = s->d_entry_offsets;
+        ei = s->d_entry_ids;
+    }
+    TannStatus st = tann_searcher_run_device(s, beam, rerank, s->d_queries, query_kind, Q, eo, ei, nullptr,
+                                             nullptr, nullptr, stream);
+    if (st != TANN_OK) return st;
+    const size_t kbytes = Q * (size_t)rerank->top_k * 4;
+    TANN_CUDA(cudaMemcpyAsync(s->h_topk_ids, s->d_topk_ids, kbytes, cudaMemcpyDeviceToHost, stream));
+    TANN_CUDA(cudaMemcpyAsync(s->h_topk_dists, s->d_topk_dists, kbytes, cudaMemcpyDeviceToHost, stream));
+    if (out_stats_host) TANN_CUDA(cudaMemcpyAsync(s->h_stats, s->d_stats, Q * 32, cudaMemcpyDeviceToHost, stream));
+    TANN_CUDA(cudaStreamSynchronize(stream));
+    memcpy(out_ids_host, s->h_topk_ids, kbytes);
+    memcpy(out_dists_host, s->h_topk_dists, kbytes);
+    if (out_stats_host) memcpy(out_stats_host, s->h_stats, Q * 32);
+    return TANN_OK;
+}
+
+TannStatus tann_searcher_destroy(TannSearcher* s) {
+    FreeSearcher(s);
+    return TANN_OK;
+}
+
+}  // extern "C"

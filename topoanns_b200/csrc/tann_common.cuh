@@ -1,0 +1,98 @@
+// Shared device helpers of the B200 graph-search kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "topoanns_b200.h"
+
+namespace tann {
+
+constexpr uint32_t kInvalid = 0xffffffffu;
+constexpr uint32_t kExpandedBit = 0x80000000u;
+constexpr uint32_t kRawMask = 0x7fffffffu;
+constexpr uint32_t kBloomWords = 1024;  // 32 768-bit filter, src/search/topology_search_kernel.cu:55
+constexpr uint32_t kCentroids = 256;
+constexpr unsigned kFull = 0xffffffffu;
+
+struct __align__(8) Cand {
+    float dist;
+    uint32_t id;
+};
+
+__host__ __device__ inline uint32_t RawId(uint32_t packed) {
+    return packed == kInvalid ? kInvalid : (packed & kRawMask);
+}
+
+// Order-preserving map float -> uint32 (total order of the reals; -0 sorts just below +0, which
+// never meets here because every distance on this path is a sum of squares or +inf).
+__device__ __forceinline__ uint32_t OrderedBits(float f) {
+    const uint32_t b = __float_as_uint(f);
+    return b ^ ((b >> 31) ? 0xffffffffu : 0x80000000u);
+}
+__device__ __forceinline__ float FromOrderedBits(uint32_t o) {
+    const uint32_t b = o ^ ((o >> 31) ? 0x80000000u : 0xffffffffu);
+    return __uint_as_float(b);
+}
+
+// 64-bit sort key of a candidate: (distance, raw id) ascending, the order of CandidateLess
+// (src/search/topology_search_kernel.cu:414-420). Invalid = (+inf, 0xffffffff) sorts last.
+__device__ __forceinline__ unsigned long long KeyOf(float dist, uint32_t packed_id) {
+    return (static_cast<unsigned long long>(OrderedBits(dist)) << 32) | RawId(packed_id);
+}
+__device__ __forceinline__ unsigned long long KeyOf(const Cand& c) { return KeyOf(c.dist, c.id); }
+
+__device__ __forceinline__ uint32_t BloomHash(int h, uint32_t v) {
+    // src/search/topology_search_kernel.cu:382-385,611-619
+    constexpr uint32_t s[6] = {0x924ed183u, 0xd854fc0au, 0xecf5e3b7u,
+                               0x1bead407u, 0x28a30449u, 0xbfc4d99fu};
+    v ^= v >> 16;
+    v *= s[h << 1];
+    v ^= v >> 13;
+    v *= s[(h << 1) + 1];
+    v ^= v >> 16;
+    return v & (kBloomWords * 32 - 1);
+}
+__device__ __forceinline__ bool BloomTest(uint32_t v, const uint32_t* words) {
+    bool ok = true;
+#pragma unroll
+    for (int h = 0; h < 3; ++h) {
+        const uint32_t bit = BloomHash(h, v);
+        ok &= ((words[bit & (kBloomWords - 1)] >> (bit >> 10)) & 1u) != 0u;
+    }
+    return ok;
+}
+__device__ __forceinline__ void BloomAdd(uint32_t v, uint32_t* words) {
+#pragma unroll
+    for (int h = 0; h < 3; ++h) {
+        const uint32_t bit = BloomHash(h, v);
+        atomicOr(&words[bit & (kBloomWords - 1)], 1u << (bit >> 10));
+    }
+}
+
+// Resolve row `n` of a sharded array; rows are `row_bytes` apart inside a shard.
+__device__ __forceinline__ const uint8_t* ShardRow(const TannShards& s, uint64_t n, uint64_t row_bytes) {
+    if (s.num_shards <= 1) return static_cast<const uint8_t*>(s.base[0]) + n * row_bytes;
+    const uint64_t shard = n / s.rows_per_shard;
+    const uint64_t local = n - shard * s.rows_per_shard;
+    return static_cast<const uint8_t*>(s.base[shard]) + local * row_bytes;
+}
+
+// The shuffle-down tree of the reference (16, 8, 4, 2, 1); lane 0 holds the result.
+__device__ __forceinline__ float WarpTreeSum(float v) {
+    v += __shfl_down_sync(kFull, v, 16);
+    v += __shfl_down_sync(kFull, v, 8);
+    v += __shfl_down_sync(kFull, v, 4);
+    v += __shfl_down_sync(kFull, v, 2);
+    v += __shfl_down_sync(kFull, v, 1);
+    return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float LoadAsFloat(const void* p, uint32_t kind, uint64_t i) {
+    if (kind == TANN_KIND_FLOAT32) return static_cast<const float*>(p)[i];
+    if (kind == TANN_KIND_UINT8) return static_cast<float>(static_cast<const uint8_t*>(p)[i]);
+    return static_cast<float>(static_cast<const int8_t*>(p)[i]);
+}
+
+}  // namespace tann

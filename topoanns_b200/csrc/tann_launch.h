@@ -1,0 +1,51 @@
+// Host-side launch functions of the kernels (internal to the library).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "topoanns_b200.h"
+
+namespace tann {
+
+struct Cand;
+struct BeamArgs;
+
+size_t BeamSmemBytes(uint32_t M, uint32_t C, uint32_t F, uint32_t L, uint32_t d);
+cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream_t stream);
+cudaError_t BeamOccupancy(uint32_t M, uint32_t slots, size_t smem, int* blocks_per_sm);
+
+cudaError_t LaunchLutBuild(const float* tables_col_major, const float* centroid,
+                           const uint32_t* chunk_offsets, uint32_t dim, uint32_t M,
+                           const void* queries, uint32_t query_kind, uint64_t Q, float* out,
+                           cudaStream_t stream);
+
+cudaError_t LaunchRvqNorms(const float* rows, uint32_t count, uint32_t dim, float* out,
+                           cudaStream_t stream);
+cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, const float* coarse,
+                             const float* coarse_t, const float* coarse_norms, uint32_t nc,
+                             const float* fine_t, const float* fine_norms, uint32_t nf,
+                             const int32_t* bucket_sizes, const uint32_t* cluster_offsets,
+                             const uint32_t* cluster_ids, uint32_t entry_count, uint32_t fallback,
+                             int32_t* out_clusters, uint32_t* out_entry_ids,
+                             uint32_t* out_entry_offsets, cudaStream_t stream);
+
+cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q, uint32_t capacity,
+                            uint32_t refine_top_l, const TannShards* base_codes,
+                            const TannShards& pq2_codes, uint32_t M, const float* lut2,
+                            const float* cross_terms, void* out, cudaStream_t stream);
+cudaError_t LaunchCrossTerms(uint32_t dim, uint32_t M, const uint32_t* chunk_offsets, const float* t1,
+                             const float* mu1, const float* t2, const float* mu2, float* out,
+                             cudaStream_t stream);
+
+cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, const void* cand,
+                         uint32_t capacity, uint64_t Q, const void* queries, uint32_t query_kind,
+                         const float* error_bounds, float* out_dists, uint32_t* out_ids,
+                         unsigned long long* out_counts, cudaStream_t stream);
+cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, uint32_t top_n,
+                           uint32_t top_k, float* out_dists, uint32_t* out_ids, cudaStream_t stream);
+
+int SmCount();
+
+}  // namespace tann
