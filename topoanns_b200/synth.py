@@ -192,9 +192,11 @@ def build_knn_graph(x: torch.Tensor, n_per: int, k: int, mem_budget: int = 1 << 
     return out
 
 
-def brute_force_topk(base: torch.Tensor, queries: torch.Tensor, k: int, batch: int = 1 << 20):
+def brute_force_topk(base: torch.Tensor, queries: torch.Tensor, k: int, batch: int = 0):
     """Exact top-k by (distance, id); returns ids [Q, k] int64 and squared distances [Q, k]."""
     Q = queries.shape[0]
+    if batch <= 0:  # keep each [Q, batch] distance block near 512 MB
+        batch = max(4096, (1 << 27) // max(Q, 1))
     dev = base.device
     best_d = torch.full((Q, k), float("inf"), device=dev)
     best_i = torch.full((Q, k), -1, dtype=torch.int64, device=dev)
