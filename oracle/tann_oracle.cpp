@@ -185,7 +185,7 @@ struct OrcBeamParams {
     uint32_t candidate_capacity;   // power of two, >= top_l
     uint32_t stop_prefix;          // = top_l unless TOPOANNS_CANDIDATE_STOP_* narrows it
     uint32_t stop_use_expanded;
-    uint32_t two_phase;            // 1: all Bloom tests of a batch, then all adds; 0: slot by slot
+    uint32_t two_phase;            // 1: per round of 128 slots all Bloom tests, then all adds; 0: slot by slot
     uint32_t reserved;
 };
 
@@ -307,16 +307,23 @@ void PushBatch(const OrcBeamParams& P, const OrcLearnedStop& ls, BeamState& s,
     const Cand inval{std::numeric_limits<float>::infinity(), kInvalid};
     std::fill(s.frontier.begin(), s.frontier.end(), inval);
     if (P.two_phase) {
-        std::vector<uint8_t> pass(nslots, 0);
-        for (uint32_t i = 0; i < nslots; ++i) {
-            const uint32_t id = ids[i];
-            pass[i] = !(id == kInvalid || id >= P.num_nodes || BloomTest(id, s.bloom.data()));
-        }
-        for (uint32_t i = 0; i < nslots; ++i) {
-            if (!pass[i]) continue;
-            s.frontier[i].id = ids[i];
-            BloomAdd(ids[i], s.bloom.data());
-            ++s.visited;
+        // The reference block has 128 threads (:59); thread t handles slots t, t+128, ... and does
+        // test-then-add on each, so within a round of 128 slots every test precedes every add, and
+        // a later round sees the adds of the earlier ones.
+        constexpr uint32_t kRound = 128;
+        std::vector<uint8_t> pass(kRound, 0);
+        for (uint32_t base = 0; base < nslots; base += kRound) {
+            const uint32_t n = std::min(kRound, nslots - base);
+            for (uint32_t i = 0; i < n; ++i) {
+                const uint32_t id = ids[base + i];
+                pass[i] = !(id == kInvalid || id >= P.num_nodes || BloomTest(id, s.bloom.data()));
+            }
+            for (uint32_t i = 0; i < n; ++i) {
+                if (!pass[i]) continue;
+                s.frontier[base + i].id = ids[base + i];
+                BloomAdd(ids[base + i], s.bloom.data());
+                ++s.visited;
+            }
         }
     } else {
         for (uint32_t i = 0; i < nslots; ++i) {

@@ -1,0 +1,59 @@
+"""Query sharding and the single top-k gather, as two gloo ranks on the CPU. Each rank searches its
+query range with the CPU checker; rank 0 must end up with exactly the unsharded result."""
+import dataclasses
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from topoanns_b200 import sharding
+
+
+def test_query_shard_covers_everything():
+    for Q in (0, 1, 7, 10, 10000):
+        for G in (1, 2, 3, 8):
+            spans = [sharding.query_shard(Q, G, r) for r in range(G)]
+            assert spans[0][0] == 0 and spans[-1][1] == Q
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(G - 1))
+            sizes = [e - b for b, e in spans]
+            assert max(sizes) - min(sizes) <= 1
+    assert sharding.rows_per_shard(1000, 8, 32) % 32 == 0 and sharding.rows_per_shard(1000, 8, 32) * 8 >= 1000
+    assert sharding.rows_per_shard(10, 4) == 3
+
+
+def _worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import pipeline
+    from topoanns_b200 import synth
+    torch.set_num_threads(1)
+    cfg = dataclasses.replace(synth.CONFIGS["cfg2"], num_nodes=4000, components=20, num_queries=51,
+                              train_sample=4000, kmeans_iters=3)
+    s = synth.build(cfg, "cpu")                        # same seed -> same replica on every rank
+    host = pipeline.index_from_synth(s)
+    q = s.queries.numpy()
+    b, e = sharding.query_shard(q.shape[0], world, rank)
+    kw = dict(top_l=32, search_width=2, max_expansions=512, top_n=32, top_k=10, entry_count=128)
+    mine = pipeline.run(host, q[b:e], **kw)
+    ids, dists = sharding.gather_topk(torch.from_numpy(mine["topk_ids"].view(np.int32)),
+                                      torch.from_numpy(mine["topk_dists"]), q.shape[0])
+    if rank == 0:
+        full = pipeline.run(host, q, **kw)
+        ok = np.array_equal(ids.numpy().view(np.uint32), full["topk_ids"]) and \
+            np.array_equal(dists.numpy().view(np.uint32), full["topk_dists"].view(np.uint32))
+        open(out_path, "w").write("ok" if ok else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_gather_equals_unsharded(tmp_path):
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    out = tmp_path / "result.txt"
+    mp.spawn(_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"

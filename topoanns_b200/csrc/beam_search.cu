@@ -6,15 +6,17 @@
 // candidate order (distance, raw id) (:414-420), same merge tie rule (:1338-1424), same selection
 // of the first W unexpanded ranks without a max_expansions re-check (:2479-2513), same ADC
 // summation tree (:656-692), same learned stop (:953-1137). Visited tests and adds of one batch
-// of slots run as two phases (all tests, barrier, all adds), which is the deterministic protocol
-// of the reference's micro-batch kernels (:2078-2106); the fused reference kernel leaves that
-// order to warp timing (:2556-2563).
+// of slots run as two phases per round of 128 slots (all tests, barrier, all adds). That is what the
+// reference's 128-thread block does in practice (each thread tests then adds its slot, round by
+// round, :2543-2564) and it is the explicit protocol of its micro-batch kernels (:2078-2106); run
+// on a B200 the compiled reference kernel agrees with this order on every query tested.
 //
 // How it differs in construction: the query's look-up table lives in shared memory (built in
 // place from the query and the PQ pivots, or staged from HBM), the Bloom filter lives in shared
 // memory, every thread owns one frontier slot (its own 4-byte adjacency load, its own 16-byte
-// code loads, a register-resident tree sum), the frontier is sorted as 64-bit keys with warp
-// shuffles, and the merge is a parallel merge-path into a second buffer instead of a
+// code loads, a register-resident tree sum), candidates and frontier entries are 64-bit keys,
+// frontier entries that cannot enter a full list are dropped before sorting, the rest are
+// rank-sorted, and the merge is a parallel merge-path into a second buffer instead of a
 // single-thread backward merge.
 
 #include "beam_args.h"
@@ -37,7 +39,14 @@ struct BeamCtl {
     uint32_t ls_prev_ids[32];
 };
 
-constexpr unsigned long long kInvalidKey = 0xff800000ffffffffull;  // KeyOf(+inf, 0xffffffff)
+// Candidates and frontier entries are 64-bit keys in shared memory: high word = order-preserving
+// bits of the distance, low word = packed node id (bit 31 = expanded). Comparing two keys with
+// bit 31 masked off is the reference's CandidateLess (distance, then raw id).
+constexpr unsigned long long kInvalidKey = 0xff800000ffffffffull;  // (+inf, 0xffffffff)
+constexpr unsigned long long kCmpMask = 0xffffffff7fffffffull;
+__device__ __forceinline__ float KeyDist(unsigned long long k) { return FromOrderedBits((uint32_t)(k >> 32)); }
+__device__ __forceinline__ uint32_t KeyPackedId(unsigned long long k) { return (uint32_t)k; }
+__device__ __forceinline__ uint32_t KeyRawId(unsigned long long k) { return RawId((uint32_t)k); }
 
 __device__ __forceinline__ uint32_t CountBitsInRange(const uint32_t* bits, uint32_t b, uint32_t e) {
     uint32_t n = 0;
@@ -56,13 +65,13 @@ __device__ __forceinline__ uint32_t FindFirstSetBit(const uint32_t* bits, uint32
 
 // Learned stop on one thread; returns true when the traversal has to stop.
 __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t valid, uint32_t visited,
-                            const Cand* cand, const uint32_t* unexp, uint32_t top_l) {
+                            const unsigned long long* cand, const uint32_t* unexp, uint32_t top_l) {
     while (s.ls_stage < ls.num_stages) {
         const uint32_t p = ls.stage_prefixes[s.ls_stage];
         if (p == 0 || p >= top_l || p < ls.top_k) { ++s.ls_stage; continue; }
         if (valid < top_l || valid < p || valid < ls.top_k || s.expanded < p) break;
-        const float dk = cand[ls.top_k - 1].dist;
-        const float boundary = cand[p - 1].dist;
+        const float dk = KeyDist(cand[ls.top_k - 1]);
+        const float boundary = KeyDist(cand[p - 1]);
         const uint32_t next64_end = min(p + 64u, top_l);
         const uint32_t next256_end = min(p + 256u, top_l);
         const uint32_t next64_span = next64_end > p ? next64_end - p : 1u;
@@ -91,7 +100,7 @@ __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t vali
                                   : 0.0f;
         f[6] = ls.feature_mask[6] ? dk : 0.0f;
         f[7] = ls.feature_mask[7] ? (boundary - dk) : 0.0f;
-        f[8] = ls.feature_mask[8] ? (cand[gap32_index].dist - dk) : 0.0f;
+        f[8] = ls.feature_mask[8] ? (KeyDist(cand[gap32_index]) - dk) : 0.0f;
         f[9] = (ls.feature_mask[9] && has_prev) ? (s.ls_prev_dk - dk) : 0.0f;
         f[10] = (ls.feature_mask[10] && has_prev) ? (s.ls_prev_boundary - boundary) : 0.0f;
         if (!ls.feature_mask[11]) {
@@ -103,7 +112,7 @@ __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t vali
         } else {
             uint32_t changed = 0;
             for (uint32_t i = 0; i < ls.top_k; ++i) {
-                const uint32_t cur = RawId(cand[i].id);
+                const uint32_t cur = KeyRawId(cand[i]);
                 bool found = false;
                 for (uint32_t j = 0; j < ls.top_k; ++j)
                     if (s.ls_prev_ids[j] == cur) { found = true; break; }
@@ -119,7 +128,7 @@ __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t vali
         s.ls_has_prev = 1;
         s.ls_topk_changed = 0;
         if (ls.feature_mask[11] && !ls.topk_churn_flag_mode)
-            for (uint32_t i = 0; i < ls.top_k; ++i) s.ls_prev_ids[i] = RawId(cand[i].id);
+            for (uint32_t i = 0; i < ls.top_k; ++i) s.ls_prev_ids[i] = KeyRawId(cand[i]);
         if (logit < ls.threshold_logit) {
             if (ls.shadow_mode) { s.ls_stage = ls.num_stages; break; }
             return true;
@@ -201,35 +210,8 @@ __device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
     }
 }
 
-// Bitonic sort of up to 128 keys, one per thread: strides below 32 by shuffle, the three strides
-// of 32 and 64 through shared memory. Returns this thread's sorted key (rank = threadIdx.x).
-__device__ __forceinline__ unsigned long long SortKeys128(unsigned long long key,
-                                                          unsigned long long* scratch) {
-    const uint32_t t = threadIdx.x;
-#pragma unroll
-    for (uint32_t k = 2; k <= 128; k <<= 1) {
-#pragma unroll
-        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
-            unsigned long long other;
-            if (j >= 32) {
-                scratch[t] = key;
-                __syncthreads();
-                other = scratch[t ^ j];
-                __syncthreads();
-            } else {
-                other = __shfl_xor_sync(kFull, key, j);
-            }
-            const bool asc = (t & k) == 0;
-            const bool lower = (t & j) == 0;
-            const bool take_min = (asc == lower);
-            key = take_min ? (key < other ? key : other) : (key > other ? key : other);
-        }
-    }
-    return key;
-}
-
-// kSingle: W * degree <= 128, so every thread owns at most one frontier slot per batch and its
-// sort key never leaves registers until the merge.
+// kSingle: W * degree <= 128, so every thread owns at most one frontier slot per batch: its key
+// stays in a register until the survivors are compacted and rank-sorted.
 template <int kM, bool kSingle>
 __global__ void __launch_bounds__(kBeamThreads)
 beam_search_kernel(const __grid_constant__ BeamArgs a) {
@@ -247,42 +229,51 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
     const uint32_t FK = kSingle ? (uint32_t)kBeamThreads : F;  // keys held in shared memory
 
     float* lut = reinterpret_cast<float*>(smem_raw);
-    Cand* cand_a = reinterpret_cast<Cand*>(lut + (size_t)M * kCentroids);
-    Cand* cand_b = cand_a + C;
-    unsigned long long* fkey = reinterpret_cast<unsigned long long*>(cand_b + C);
-    uint32_t* bloom = reinterpret_cast<uint32_t*>(fkey + FK);
+    unsigned long long* cand_a = reinterpret_cast<unsigned long long*>(lut + (size_t)M * kCentroids);
+    unsigned long long* cand_b = cand_a + C;
+    unsigned long long* fkey = cand_b + C;        // frontier keys (compacted survivors when kSingle)
+    unsigned long long* skey = fkey + FK;         // sorted frontier (kSingle only)
+    uint32_t* bloom = reinterpret_cast<uint32_t*>(skey + (kSingle ? FK : 0));
     uint32_t* unexp = bloom + kBloomWords;
     uint32_t* offs = unexp + UW;
     float* sq = reinterpret_cast<float*>(offs + M + 1);
 
     __shared__ BeamCtl ctl;
+    __shared__ uint32_t s_surv;
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31;
-    const Cand inval{__int_as_float(0x7f800000), kInvalid};
 
     for (uint64_t q = blockIdx.x; q < a.num_queries; q += gridDim.x) {
         // ---- per-query set-up --------------------------------------------------------------
         if (a.lut != nullptr) {
             const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
             float4* dst = reinterpret_cast<float4*>(lut);
+#pragma unroll 4
             for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
         } else {
-            // src/search/pq_query_tables.cu:33-52, one table entry per thread per step
+            // src/search/pq_query_tables.cu:33-52
             for (uint32_t i = tid; i < d; i += kBeamThreads)
                 sq[i] = LoadAsFloat<float>(a.queries, a.query_kind, q * d + i) - __ldg(a.ix.pq_centroid + i);
             for (uint32_t i = tid; i <= M; i += kBeamThreads) offs[i] = __ldg(a.ix.pq_chunk_offsets + i);
             __syncthreads();
-            for (uint32_t e = tid; e < M * kCentroids; e += kBeamThreads) {
-                const uint32_t m = e >> 8, c = e & 255u;
-                float acc = 0.0f;
+            // Four consecutive centroids per thread and step: one 16-byte load per dim, the same
+            // per-entry FMA chain (ascending dim) as the one-entry form.
+#pragma unroll 4
+            for (uint32_t item = tid; item < M * (kCentroids / 4); item += kBeamThreads) {
+                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
-                    const float diff = __ldg(a.ix.pq_tables_col_major + (size_t)dim * kCentroids + c) - sq[dim];
-                    acc = fmaf(diff, diff, acc);
+                    const float4 t = __ldg(reinterpret_cast<const float4*>(a.ix.pq_tables_col_major + (size_t)dim * kCentroids + c4));
+                    const float sv = sq[dim];
+                    float df = t.x - sv; acc.x = fmaf(df, df, acc.x);
+                    df = t.y - sv; acc.y = fmaf(df, df, acc.y);
+                    df = t.z - sv; acc.z = fmaf(df, df, acc.z);
+                    df = t.w - sv; acc.w = fmaf(df, df, acc.w);
                 }
-                lut[e] = acc;
+                *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
             }
         }
-        for (uint32_t i = tid; i < C; i += kBeamThreads) { cand_a[i] = inval; cand_b[i] = inval; }
+        for (uint32_t i = tid; i < C; i += kBeamThreads) { cand_a[i] = kInvalidKey; cand_b[i] = kInvalidKey; }
         for (uint32_t i = tid; i < kBloomWords; i += kBeamThreads) bloom[i] = 0u;
         for (uint32_t i = tid; i < UW; i += kBeamThreads) unexp[i] = 0u;
         if (tid == 0) {
@@ -292,14 +283,15 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             ctl.ls_stage = 0; ctl.ls_has_prev = 0; ctl.ls_topk_changed = 0;
             ctl.ls_prev_dk = __int_as_float(0x7f800000);
             ctl.ls_prev_boundary = __int_as_float(0x7f800000);
+            s_surv = 0;
         }
         if (tid < 32) ctl.ls_prev_ids[tid] = kInvalid;
         __syncthreads();
 
         // block-uniform state, identical in every thread
         uint32_t valid = 0, visited = 0, hash_iter = 0;
-        Cand* cur = cand_a;
-        Cand* nxt = cand_b;
+        unsigned long long* cur = cand_a;
+        unsigned long long* nxt = cand_b;
         const uint32_t entry_begin = a.entry_offsets[q];
         const uint32_t num_entries = a.entry_offsets[q + 1] - entry_begin;
         const uint32_t entry_batches = slots == 0 ? 0 : (num_entries + slots - 1) / slots;
@@ -342,9 +334,10 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                                     word &= word - 1u;
                                     unexp[w] &= ~(1u << bit);
                                     if (idx >= C || idx >= L || idx >= valid) continue;
-                                    const uint32_t pid = cur[idx].id;
+                                    const unsigned long long k = cur[idx];
+                                    const uint32_t pid = KeyPackedId(k);
                                     if (pid == kInvalid || (pid & kExpandedBit)) continue;
-                                    cur[idx].id = pid | kExpandedBit;
+                                    cur[idx] = k | kExpandedBit;
                                     ctl.selected[nsel++] = pid & kRawMask;
                                     ++ctl.expanded;
                                 }
@@ -387,9 +380,19 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 const bool pass = id != kInvalid && id < N && !BloomTest(id, bloom);
                 // Park the surviving id in the key slot; phase 2 turns it into a key.
                 const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
-                if (kSingle) my_key = parked; else if (s < F) fkey[s] = parked;
+                if (kSingle) {
+                    my_key = parked;
+                } else {
+                    // More slots than threads: the reference's 128 threads walk the slots in rounds
+                    // of 128, so the tests of a round see the adds of the rounds before it
+                    // (src/search/topology_search_kernel.cu:2543-2564). Same here, made explicit.
+                    if (s < F) fkey[s] = parked;
+                    __syncthreads();
+                    if (pass) BloomAdd(id, bloom);
+                    __syncthreads();
+                }
             }
-            __syncthreads();  // every test of the batch precedes every add
+            if (kSingle) __syncthreads();  // every test of the round precedes every add
             // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
             uint32_t fv = 0;
             for (uint32_t r = 0; r < rounds; ++r) {
@@ -398,33 +401,61 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 const bool pass = parked != kInvalidKey;
                 if (pass) {
                     const uint32_t id = (uint32_t)parked;
-                    BloomAdd(id, bloom);
+                    if (kSingle) BloomAdd(id, bloom);
                     const uint8_t* row = ShardRow(a.ix.codes, id, M);
                     const float dist = AdcTreeThread<kM>(lut, row, M);
-                    const unsigned long long key = KeyOf(dist, id);
+                    const unsigned long long key = ((unsigned long long)OrderedBits(dist) << 32) | id;
                     if (kSingle) my_key = key; else fkey[s] = key;
                 }
                 fv += __syncthreads_count(pass);
             }
+            const uint32_t nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
 
-            // ---- sort the frontier ---------------------------------------------------------------
+            // ---- order the frontier -----------------------------------------------------------
+            // sorted[0 .. n) = the frontier entries that can still enter the list, ascending.
+            const unsigned long long* sorted;
+            uint32_t n;
             if (kSingle) {
-                my_key = SortKeys128(my_key, fkey);
-                fkey[tid] = my_key;  // rank = thread index; invalid keys sort last
+                // When the list is full an entry not below its last element can never be accepted
+                // (the acceptance test below compares entry a with element nv-1-a), so only the
+                // others are kept; they are compacted and rank-sorted (each survivor counts the
+                // survivors in front of it), which costs ~4 instructions per pair instead of a
+                // 28-step bitonic network over all 128 slots.
+                const unsigned long long thr = valid == C ? (cur[C - 1] & kCmpMask) : ~0ull;
+                const bool surv = my_key != kInvalidKey && my_key < thr;
+                const uint32_t ballot = __ballot_sync(kFull, surv);
+                uint32_t base = 0;
+                if (lane == 0 && ballot != 0u) base = atomicAdd(&s_surv, (uint32_t)__popc(ballot));
+                base = __shfl_sync(kFull, base, 0);
+                if (surv) fkey[base + __popc(ballot & ((1u << lane) - 1u))] = my_key;
                 __syncthreads();
+                n = s_surv;
+                if (tid < n) {
+                    const unsigned long long k = fkey[tid];
+                    uint32_t rank = 0;
+                    for (uint32_t j = 0; j < n; ++j) {
+                        const unsigned long long kj = fkey[j];
+                        rank += (kj < k || (kj == k && j < tid)) ? 1u : 0u;
+                    }
+                    skey[rank] = k;
+                }
+                __syncthreads();
+                if (tid == 0) s_surv = 0;
+                sorted = skey;
             } else {
                 SortKeysShared(fkey, F);
+                sorted = fkey;
+                n = fv;
             }
 
             // ---- merge (:1338-1424) as a parallel merge-path --------------------------------------
-            const uint32_t nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
             uint32_t accepted = 0;
             {
-                const uint32_t lim = min(fv, nv);
+                const uint32_t lim = min(n, nv);
                 for (uint32_t base = 0; base < lim; base += kBeamThreads) {
                     const uint32_t x = base + tid;
                     bool pred = false;
-                    if (x < lim) pred = fkey[x] < KeyOf(cur[nv - 1 - x]);
+                    if (x < lim) pred = sorted[x] < (cur[nv - 1 - x] & kCmpMask);
                     const uint32_t cnt = __syncthreads_count(pred);
                     accepted += cnt;
                     if (cnt < (uint32_t)kBeamThreads) break;  // the predicate is monotone in x
@@ -433,32 +464,29 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             if (accepted != 0) {
                 const uint32_t kept = nv - accepted;
                 for (uint32_t i = tid; i < kept; i += kBeamThreads) {
-                    const Cand c = cur[i];
-                    const unsigned long long ck = KeyOf(c);
+                    const unsigned long long c = cur[i];
+                    const unsigned long long ck = c & kCmpMask;
                     uint32_t lo = 0, hi = accepted;  // frontier keys <= ck go in front of it
                     while (lo < hi) {
                         const uint32_t mid = (lo + hi) >> 1;
-                        if (fkey[mid] <= ck) lo = mid + 1; else hi = mid;
+                        if (sorted[mid] <= ck) lo = mid + 1; else hi = mid;
                     }
                     nxt[i + lo] = c;
                 }
                 bool changed = false;
                 for (uint32_t j = tid; j < accepted; j += kBeamThreads) {
-                    const unsigned long long fk = fkey[j];
+                    const unsigned long long fk = sorted[j];
                     uint32_t lo = 0, hi = kept;  // kept candidates < fk stay in front of it
                     while (lo < hi) {
                         const uint32_t mid = (lo + hi) >> 1;
-                        if (KeyOf(cur[mid]) < fk) lo = mid + 1; else hi = mid;
+                        if ((cur[mid] & kCmpMask) < fk) lo = mid + 1; else hi = mid;
                     }
-                    Cand c;
-                    c.dist = FromOrderedBits((uint32_t)(fk >> 32));
-                    c.id = (uint32_t)fk;
-                    nxt[j + lo] = c;
+                    nxt[j + lo] = fk;
                     changed |= (j + lo) < a.p.learned_stop.top_k;
                 }
-                for (uint32_t i = nv + tid; i < C; i += kBeamThreads) nxt[i] = inval;
+                for (uint32_t i = nv + tid; i < C; i += kBeamThreads) nxt[i] = kInvalidKey;
                 if (changed) ctl.ls_topk_changed = 1;
-                Cand* t = cur; cur = nxt; nxt = t;
+                unsigned long long* t = cur; cur = nxt; nxt = t;
             }
             valid = nv;
             visited += fv;
@@ -477,7 +505,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 const uint32_t i = base + tid;
                 bool un = false;
                 if (i < prefix) {
-                    const uint32_t pid = cur[i].id;
+                    const uint32_t pid = KeyPackedId(cur[i]);
                     if (pid != kInvalid) {
                         un = (pid & kExpandedBit) == 0;
                         if (rebuild) BloomAdd(pid & kRawMask, bloom);
@@ -496,7 +524,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
         // ---- results -----------------------------------------------------------------------------
         Cand* out = a.out_cand + q * (uint64_t)C;
-        for (uint32_t i = tid; i < C; i += kBeamThreads) out[i] = cur[i];
+        for (uint32_t i = tid; i < C; i += kBeamThreads) {
+            const unsigned long long k = cur[i];
+            Cand c;
+            c.dist = KeyDist(k);
+            c.id = KeyPackedId(k);
+            out[i] = c;
+        }
         if (tid == 0) {
             uint32_t* st = a.out_stats + q * 8;
             st[0] = visited; st[1] = ctl.expanded; st[2] = 0; st[3] = ctl.iterations;
@@ -508,7 +542,8 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
 size_t BeamSmemBytes(uint32_t M, uint32_t C, uint32_t F, uint32_t L, uint32_t d) {
     const size_t uw = (L + 31) / 32;
-    const size_t fk = F <= (uint32_t)kBeamThreads ? (size_t)kBeamThreads : F;
+    // single-round kernels keep two 128-key buffers (compacted and sorted frontier)
+    const size_t fk = F <= (uint32_t)kBeamThreads ? (size_t)2 * kBeamThreads : F;
     size_t bytes = (size_t)M * kCentroids * 4 + (size_t)2 * C * 8 + fk * 8 + kBloomWords * 4 +
                    uw * 4 + ((size_t)M + 1) * 4 + (size_t)d * 4;
     return (bytes + 15) & ~(size_t)15;

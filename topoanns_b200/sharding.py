@@ -1,0 +1,103 @@
+"""Partitioning of the path over the GPUs of one box (one process per GPU).
+
+* Replicated index, queries sharded: rank r owns queries [r*Q/G, (r+1)*Q/G); no communication while
+  searching; the final top-k lists go to one rank with a single gather.
+* Node-id-range shards (indices larger than one GPU): node n lives on rank n // rows_per_shard;
+  adjacency, codes and vector pages are split by the same ranges and every rank maps its peers'
+  shard buffers (CUDA IPC), so the search kernel reads remote rows with ordinary loads over NVLink.
+  Queries stay sharded by rank, so the gather above is still the only collective.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+def query_shard(num_queries: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous query range of `rank` (sizes differ by at most one)."""
+    base, extra = divmod(num_queries, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def rows_per_shard(num_nodes: int, world_size: int, vectors_per_page: int = 1) -> int:
+    """Nodes per shard, rounded up so that a vector page never straddles two shards."""
+    rows = (num_nodes + world_size - 1) // world_size
+    vpp = max(1, vectors_per_page)
+    return (rows + vpp - 1) // vpp * vpp
+
+
+def gather_topk(ids: torch.Tensor, dists: torch.Tensor, num_queries: int, dst: int = 0):
+    """One gather of the per-rank [Q_r, k] id / distance lists to `dst`; returns the [Q, k] lists there
+    (None elsewhere). Shards are padded to the largest shard so a single collective suffices."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    k = ids.shape[1]
+    longest = max(query_shard(num_queries, world, r)[1] - query_shard(num_queries, world, r)[0] for r in range(world))
+    packed = torch.full((longest, 2 * k), -1, dtype=torch.int32, device=ids.device)
+    n = ids.shape[0]
+    packed[:n, :k] = ids.to(torch.int32)
+    packed[:n, k:] = dists.contiguous().view(torch.int32)
+    out = [torch.empty_like(packed) for _ in range(world)] if rank == dst else None
+    dist.gather(packed, out, dst=dst)
+    if rank != dst:
+        return None, None
+    all_ids, all_d = [], []
+    for r, t in enumerate(out):
+        b, e = query_shard(num_queries, world, r)
+        all_ids.append(t[: e - b, :k])
+        all_d.append(t[: e - b, k:].contiguous().view(torch.float32))
+    return torch.cat(all_ids), torch.cat(all_d)
+
+
+class PeerBuffers:
+    """One shard buffer per rank for one array, allocated through the C ABI and mapped into every rank."""
+
+    def __init__(self, local_bytes: int):
+        self.lib = capi.load()
+        self.world, self.rank = dist.get_world_size(), dist.get_rank()
+        ptr = C.c_void_p()
+        capi.check(self.lib.tann_device_alloc(max(local_bytes, 256), C.byref(ptr)))
+        self.local = ptr.value
+        handle = C.create_string_buffer(capi.IPC_HANDLE_BYTES)
+        capi.check(self.lib.tann_ipc_export(C.c_void_p(self.local), handle))
+        mine = torch.tensor(list(handle.raw), dtype=torch.uint8, device="cuda")
+        every = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(every, mine)
+        self.bases: List[int] = []
+        self._opened = []
+        for r, h in enumerate(every):
+            if r == self.rank:
+                self.bases.append(self.local)
+                continue
+            p = C.c_void_p()
+            capi.check(self.lib.tann_ipc_open(bytes(h.cpu().numpy().tobytes()), C.byref(p)))
+            self.bases.append(p.value)
+            self._opened.append(p.value)
+
+    def local_tensor(self, nbytes: int) -> torch.Tensor:
+        """uint8 view of the local shard (for filling it with torch ops)."""
+        return _tensor_from_ptr(self.local, nbytes)
+
+    def close(self):
+        dist.barrier()
+        for p in self._opened:
+            self.lib.tann_ipc_close(C.c_void_p(p))
+        self._opened = []
+        dist.barrier()
+        if self.local:
+            self.lib.tann_device_free(C.c_void_p(self.local))
+            self.local = 0
+
+
+def _tensor_from_ptr(ptr: int, nbytes: int) -> torch.Tensor:
+    """Wrap raw device memory as a uint8 torch tensor through the CUDA array interface."""
+
+    class _Holder:
+        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+    return torch.as_tensor(_Holder(), device="cuda")
