@@ -262,6 +262,10 @@ def main():
     t0 = time.perf_counter()
     for _ in range(args.steps):
         ids, dists, _ = sr.run_host(q_pinned.numpy(), tp, rp)
+        if world > 1:  # the one collective of the path: final top-k lists to rank 0
+            from topoanns_b200 import sharding
+            sharding.gather_topk(torch.from_numpy(ids.view(np.int32)).to(device), torch.from_numpy(dists).to(device),
+                                 Q * world)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()

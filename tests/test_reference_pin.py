@@ -166,20 +166,34 @@ def test_reference_pq2_refine_and_bound_filter(tmp_path):
     entries = np.full((Q, 1), s.medoid, np.uint32)
     _write_index(tmp_path, s, host, entries)
     q = s.queries.cpu().numpy()
-    for mode, tile, bound in (("tiled", 16, 1), ("page", 1, 1), ("tiled", 16, 0), ("linear", 16, 0)):
-        tag = f"pq2_{mode}_{bound}"
-        _run(tmp_path, tag, "fused", 64, 2, 2048, 10, 64, mode, tile, 1, bound)
+    # traversal with M = 48 (two tree groups) and float32 exact rerank without pq2
+    _run(tmp_path, "t48", "search", 64, 2, 2048, 10, 64, "linear", 16, 0, 0, 1)
+    lut = orc.lut_build(q, host["pq_tables"], host["pq_centroid"], host["pq_chunk_offsets"])
+    cand, st = orc.beam_search(host["adjacency"], host["codes"], lut, np.arange(Q + 1, dtype=np.uint32), entries.reshape(-1),
+                               top_l=64, search_width=2, max_expansions=2048, capacity=64)
+    rid0 = _load(tmp_path, "t48", "search0_ids", np.uint32).reshape(Q, 64)
+    rd0 = _load(tmp_path, "t48", "search0_dist", np.float32).reshape(Q, 64)
+    trav_same = float(((rid0 == cand[:, :, 1]) & (rd0.view(np.uint32) == cand[:, :, 0])).all(1).mean())
+    _report("traversal_m48", {"identical": trav_same})
+    failures = []
+    if trav_same < 0.99:
+        failures.append(f"traversal M=48 {trav_same}")
+    for mode, tile, pq2, bound in (("linear", 16, 0, 0), ("tiled", 16, 1, 0), ("linear", 16, 1, 0), ("tiled", 16, 1, 1),
+                                   ("page", 1, 1, 1)):
+        tag = f"pq2_{mode}_{pq2}_{bound}"
+        _run(tmp_path, tag, "fused", 64, 2, 2048, 10, 64, mode, tile, pq2, bound)
         rid = _load(tmp_path, tag, "rerank_ids", np.uint32).reshape(Q, 64)
         rdist = _load(tmp_path, tag, "rerank_dist", np.float32).reshape(Q, 64)
         rstats = _load(tmp_path, tag, "rerank_stats", np.uint64)
         ref = pipeline.run(host, q, top_l=64, search_width=2, max_expansions=2048, top_n=64, top_k=10,
-                           fixed_entries=[s.medoid], use_pq2=True, refine_top_l=64, bound_filter=bool(bound),
+                           fixed_entries=[s.medoid], use_pq2=bool(pq2), refine_top_l=64, bound_filter=bool(bound),
                            tile=0 if mode == "linear" else tile)
         same = (rid == ref["ids"]).all(1)
-        _report("pq2", {"mode": mode, "bound": bound, "rows_identical": float(same.mean()),
-                        "ref_exact": int(rstats[1]), "ref_filtered": int(rstats[2]),
+        dist_same = float((rdist[same].view(np.uint32) == ref["dists"][same].view(np.uint32)).mean()) if same.any() else 0.0
+        top10 = float((rid[:, :10] == ref["topk_ids"]).all(1).mean())
+        _report("pq2", {"mode": mode, "pq2": pq2, "bound": bound, "rows_identical": float(same.mean()), "top10_identical": top10,
+                        "dist_bits_identical": dist_same, "ref_exact": int(rstats[1]), "ref_filtered": int(rstats[2]),
                         "checker_exact": ref["n_exact"], "checker_filtered": ref["n_filtered"]})
-        assert float(same.mean()) >= 0.95
-        np.testing.assert_allclose(rdist[same], ref["dists"][same], rtol=1e-5)
-        if float(same.mean()) == 1.0:
-            assert int(rstats[2]) == ref["n_filtered"]
+        if float(same.mean()) < 0.99:
+            failures.append(f"{tag}: rows identical {float(same.mean()):.3f}")
+    assert not failures, failures

@@ -57,3 +57,53 @@ def test_two_ranks_gather_equals_unsharded(tmp_path):
     out = tmp_path / "result.txt"
     mp.spawn(_worker, args=(2, port, str(out)), nprocs=2, join=True)
     assert out.read_text() == "ok"
+
+
+def _sharded_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import pipeline
+    from topoanns_b200 import synth, synth_sharded
+    torch.set_num_threads(1)
+    cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=6000, components=24, num_queries=40,
+                              train_sample=3000, kmeans_iters=3)
+    sh = synth_sharded.build(cfg, "cpu")
+    whole = synth_sharded.gather_whole(sh)
+    problems = []
+    N = whole.vectors.shape[0]
+    if N != sh.total_nodes or sh.rows_per_shard * world != N or sh.rows_per_shard % 32:
+        problems.append("shard sizes")
+    if int(whole.adjacency.min()) < 0 or int(whole.adjacency.max()) >= N:
+        problems.append("adjacency range")
+    # kNN neighbours of a node are spread over both shards
+    nbr_owner = (whole.adjacency[:, :cfg.knn_edges].long() // sh.rows_per_shard).float().mean().item()
+    if not 0.3 < nbr_owner < 0.7:
+        problems.append(f"neighbours not scattered ({nbr_owner})")
+    x = whole.vectors.float()
+    want = (torch.cdist(whole.queries, x) ** 2).topk(10, largest=False).values
+    got = ((x[whole.gt_ids] - whole.queries.unsqueeze(1)) ** 2).sum(2)
+    if not torch.allclose(got, want):
+        problems.append("ground truth")
+    sizes, offsets, ids = whole.rvq_buckets
+    if int(sizes.sum()) != N or int(offsets[-1]) != ids.numel():
+        problems.append("rvq buckets")
+    if rank == 0:
+        host = pipeline.index_from_synth(whole)
+        r = pipeline.run(host, whole.queries.numpy(), top_l=64, search_width=2, max_expansions=2048, top_n=64,
+                         top_k=10, entry_count=128)
+        rec = synth.recall_at_k(r["topk_ids"], whole.gt_ids.numpy(), 10)
+        if rec < 0.6:
+            problems.append(f"recall {rec}")
+        open(out_path, "w").write("ok" if not problems else "; ".join(problems))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_node_range_sharded_generator(tmp_path):
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    out = tmp_path / "result.txt"
+    mp.spawn(_sharded_worker, args=(2, port, str(out)), nprocs=2, join=True)
+    assert out.read_text() == "ok"
