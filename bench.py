@@ -34,7 +34,7 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 L_SWEEP = (16, 32, 64, 128, 256, 512, 1024)
-TOPN_SWEEP = (32, 128, 512)
+TOPN_SWEEP = (32, 128, 256, 512)
 RECALL_TARGET = 0.95
 
 
@@ -221,7 +221,7 @@ def main():
     if args.top_l:
         points = [(args.top_l, args.top_n or 32)]
     else:
-        points = [(L, 32) for L in L_SWEEP] + [(L, tn) for tn in TOPN_SWEEP[1:] for L in (16, 64, 256)]
+        points = [(L, 32) for L in L_SWEEP] + [(L, tn) for tn in TOPN_SWEEP[1:] for L in (16, 32, 64)]
     for L, tn in points:
         run_point(L, tn)  # warm
         ids, stats, dt, _, _ = run_point(L, tn)
@@ -332,7 +332,7 @@ def main():
                                    "bytes_per_query": beam_bytes / Q}},
         "e2e": {"value": total_q / (e2e_ms * 1e-3), "unit": "queries/s",
                 "h2d_bytes_per_step": int(q_host.nbytes), "d2h_bytes_per_step": int(Q * 10 * 8)},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": 5 * args.steps,  # rvq, beam, float->uint8 check, rerank, top-k pack
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_source": peak_src, "kernel": "beam_search_kernel",

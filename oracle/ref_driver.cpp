@@ -199,6 +199,28 @@ int main(int argc, char** argv) {
             }
             DumpRerank(prefix, rr, out.rerank_stats, params.rerank.top_n);
             Dump(prefix, "search0_stats", stats);
+        } else if (mode == "pq2refine") {
+            // traversal on the device, then the pq2 refine stage alone; dumps the refined lists
+            DeviceEntryBatch batch;
+            batch.num_queries = nq;
+            batch.entries_per_query = ecount;
+            std::vector<std::uint32_t> offsets(nq + 1), flat;
+            for (std::uint32_t q = 0; q <= nq; ++q) offsets[q] = q * ecount;
+            for (const auto& e : entries) flat.insert(flat.end(), e.begin(), e.end());
+            batch.offsets = CudaBuffer<std::uint32_t>::CopyFromHost(offsets);
+            batch.ids = CudaBuffer<std::uint32_t>::CopyFromHost(flat);
+            const auto oracle = PqDistanceOracle::FromFloatQueries(res, queries, nq);
+            TopologySearchParams tp = params.topology;
+            tp.candidate_queue_size = std::max(tp.top_l, params.rerank.top_n);
+            const auto topo = detail::RunTopologySearchKernelBatchDevice(res, oracle, batch, tp);
+            const auto refined = detail::RunPq2RefineBatchDevice(res, topo, queries, nq, params.topology.top_l);
+            const auto host = refined.candidate_buffer.CopyToHost();
+            std::vector<float> dist;
+            std::vector<std::uint32_t> ids;
+            for (const auto& c : host) { dist.push_back(c.distance); ids.push_back(c.node_id); }
+            Dump(prefix, "refined_dist", dist);
+            Dump(prefix, "refined_ids", ids);
+            std::cout << "traversal_kernel_ms=" << topo.kernel_ms << " pq2_refine_kernel_ms=" << refined.kernel_ms << "\n";
         } else {
             std::cerr << "unknown mode " << mode << "\n";
             return 2;

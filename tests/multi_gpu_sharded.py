@@ -1,0 +1,72 @@
+"""Node-id-range sharding on real peers: run with
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 tests/multi_gpu_sharded.py
+Every rank holds one shard (adjacency, codes, vector pages) in IPC-shared device memory, searches its
+own slice of the queries reading remote rows over NVLink, and rank 0 gathers the top-k lists. The
+result must equal (a) the same search on an unsharded copy of the whole index held by rank 0 and
+(b) the CPU checker. Not collected by pytest (needs >= 2 GPUs); NVLS is switched off so that a rank
+that dies cannot disturb its peers."""
+import dataclasses
+import os
+import sys
+
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from oracle import pipeline
+    from topoanns_b200 import search, sharding, synth, synth_sharded
+    nodes = int(os.environ.get("TANN_NODES", "400000"))
+    cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=nodes, components=max(world, nodes // 1000),
+                              num_queries=1000, kmeans_iters=5, train_sample=65536)
+    sh = synth_sharded.build(cfg, f"cuda:{local}")
+    ix, buffers = sharding.peer_index_from_sharded(sh)
+    model = search.RvqModel(dim=cfg.dim, coarse=sh.rvq_coarse.contiguous(), fine=sh.rvq_fine.contiguous(),
+                            bucket_sizes=sh.rvq_buckets[0], cluster_offsets=sh.rvq_buckets[1], cluster_ids=sh.rvq_buckets[2])
+    Q = sh.queries.shape[0]
+    b, e = sharding.query_shard(Q, world, rank)
+    sr = search.Searcher(ix, max(e - b, 1), 128, 64, 128)
+    sr.set_rvq(model, 128)
+    tp = search.TopologySearchParams(top_l=64, search_width=2, max_expansions=4096)
+    rp = search.RerankExactParams(top_k=10, top_n=32)
+    qn = sh.queries.cpu().numpy()
+    ids, dists, stats = sr.run_host(qn[b:e], tp, rp, want_stats=True)
+    all_ids, all_d = sharding.gather_topk(torch.from_numpy(ids.view(np.int32)).cuda(), torch.from_numpy(dists).cuda(), Q)
+    whole = synth_sharded.gather_whole(sh)
+    ok = True
+    if rank == 0:
+        got_ids, got_d = all_ids.cpu().numpy().view(np.uint32), all_d.cpu().numpy()
+        full_ix = search.device_index_from_synth(whole)
+        full_model = search.rvq_model_from_synth(whole)
+        sr2 = search.Searcher(full_ix, Q, 128, 64, 128)
+        sr2.set_rvq(full_model, 128)
+        ids2, d2, _ = sr2.run_host(qn, tp, rp)
+        ref = pipeline.run(pipeline.index_from_synth(whole), qn, top_l=64, search_width=2, max_expansions=4096, top_n=32,
+                           top_k=10, entry_count=128)
+        same_unsharded = np.array_equal(got_ids, ids2) and np.array_equal(got_d.view(np.uint32), d2.view(np.uint32))
+        same_checker = np.array_equal(got_ids, ref["topk_ids"]) and np.array_equal(got_d.view(np.uint32), ref["topk_dists"].view(np.uint32))
+        rec = synth.recall_at_k(got_ids, whole.gt_ids.cpu().numpy(), 10)
+        remote = 1.0 - 1.0 / world
+        print(f"sharded x{world}: nodes={sh.total_nodes} identical_to_unsharded={same_unsharded} identical_to_checker={same_checker} "
+              f"recall@10={rec:.3f} expected_remote_fraction={remote:.3f}")
+        ok = same_unsharded and same_checker
+        sr2.close()
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.broadcast(flag, 0)
+    sr.close()
+    for pb in buffers.values():
+        pb.close()
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

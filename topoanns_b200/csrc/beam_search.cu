@@ -304,15 +304,19 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             if (in_entries) {
                 nslots = slots;
             } else {
-                // stop tests and selection on one thread (:2414-2513)
-                if (tid == 0) {
+                // stop tests and selection by warp 0 (:2414-2513). The unexpanded bitmap was rebuilt
+                // from the list after the last merge, so every set bit is a valid, unexpanded rank
+                // below min(valid, L): the first W set bits are exactly what the reference's serial
+                // scan picks, and they can be found with one popcount scan over the words.
+                if (tid < 32) {
                     uint32_t stop = 0, nsel = 0;
-                    if (ctl.expanded >= a.p.max_expansions || valid == 0) {
-                        stop = 1;
-                    } else if (a.p.learned_stop.enabled &&
-                               LearnedStop(a.p.learned_stop, ctl, valid, visited, cur, unexp, L)) {
-                        stop = 1;
-                    } else {
+                    if (lane == 0) {
+                        if (ctl.expanded >= a.p.max_expansions || valid == 0) stop = 1;
+                        else if (a.p.learned_stop.enabled &&
+                                 LearnedStop(a.p.learned_stop, ctl, valid, visited, cur, unexp, L)) stop = 1;
+                    }
+                    stop = __shfl_sync(kFull, stop, 0);
+                    if (!stop) {
                         const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
                         bool any = false;
                         if (prefix_stop && a.p.stop_use_expanded) {
@@ -320,33 +324,63 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         } else {
                             const uint32_t words = (prefix_stop && valid >= a.p.stop_prefix)
                                                        ? (a.p.stop_prefix + 31) / 32 : UW;
-                            for (uint32_t w = 0; w < words; ++w) any |= unexp[w] != 0u;
+                            bool mine = false;
+                            for (uint32_t w = lane; w < words; w += 32) mine |= unexp[w] != 0u;
+                            any = __ballot_sync(kFull, mine) != 0u;
                         }
                         if (!any) {
                             stop = 1;
+                        } else if (UW <= 32) {
+                            const uint32_t word = lane < UW ? unexp[lane] : 0u;
+                            const uint32_t cnt = __popc(word);
+                            uint32_t incl = cnt;
+#pragma unroll
+                            for (int off = 1; off < 32; off <<= 1) {
+                                const uint32_t t = __shfl_up_sync(kFull, incl, off);
+                                if (lane >= (uint32_t)off) incl += t;
+                            }
+                            const uint32_t excl = incl - cnt;
+                            nsel = min(__shfl_sync(kFull, incl, 31), W);
+                            uint32_t w = word;
+                            for (uint32_t sidx = excl; sidx < min(incl, nsel); ++sidx) {
+                                const uint32_t bit = __ffs(w) - 1;
+                                w &= w - 1u;
+                                const uint32_t idx = lane * 32 + bit;
+                                const unsigned long long k = cur[idx];
+                                cur[idx] = k | kExpandedBit;
+                                ctl.selected[sidx] = KeyPackedId(k) & kRawMask;
+                            }
+                            if (w != word) unexp[lane] = w;
+                            if (lane == 0) { ++ctl.iterations; ctl.expanded += nsel; }
+                            if (nsel == 0) stop = 1;
                         } else {
-                            ++ctl.iterations;
-                            for (uint32_t w = 0; w < UW && nsel < W; ++w) {
-                                uint32_t word = unexp[w];
-                                while (word != 0u && nsel < W) {
-                                    const uint32_t bit = __ffs(word) - 1;
-                                    const uint32_t idx = w * 32 + bit;
-                                    word &= word - 1u;
-                                    unexp[w] &= ~(1u << bit);
-                                    if (idx >= C || idx >= L || idx >= valid) continue;
-                                    const unsigned long long k = cur[idx];
-                                    const uint32_t pid = KeyPackedId(k);
-                                    if (pid == kInvalid || (pid & kExpandedBit)) continue;
-                                    cur[idx] = k | kExpandedBit;
-                                    ctl.selected[nsel++] = pid & kRawMask;
-                                    ++ctl.expanded;
+                            if (lane == 0) {
+                                ++ctl.iterations;
+                                for (uint32_t w = 0; w < UW && nsel < W; ++w) {
+                                    uint32_t word = unexp[w];
+                                    while (word != 0u && nsel < W) {
+                                        const uint32_t bit = __ffs(word) - 1;
+                                        const uint32_t idx = w * 32 + bit;
+                                        word &= word - 1u;
+                                        unexp[w] &= ~(1u << bit);
+                                        if (idx >= C || idx >= L || idx >= valid) continue;
+                                        const unsigned long long k = cur[idx];
+                                        const uint32_t pid = KeyPackedId(k);
+                                        if (pid == kInvalid || (pid & kExpandedBit)) continue;
+                                        cur[idx] = k | kExpandedBit;
+                                        ctl.selected[nsel++] = pid & kRawMask;
+                                        ++ctl.expanded;
+                                    }
                                 }
                             }
+                            nsel = __shfl_sync(kFull, nsel, 0);
                             if (nsel == 0) stop = 1;
                         }
                     }
-                    ctl.stop = stop;
-                    ctl.nsel = nsel;
+                    if (lane == 0) {
+                        ctl.stop = stop;
+                        ctl.nsel = nsel;
+                    }
                 }
                 __syncthreads();
                 if (ctl.stop) break;

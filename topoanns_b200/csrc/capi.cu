@@ -354,6 +354,8 @@ struct TannSearcher {
     // device work space
     void* d_queries;          // max_queries * dim * 4
     float* d_queries_f32;     // float copy of the queries for RVQ / pq2 when the kind is not float
+    uint8_t* d_queries_u8;    // uint8 copy of integer-valued float queries (integer rerank path)
+    uint32_t* d_not_u8;       // set by the conversion kernel when a value is not an integer in [0, 255]
     uint32_t* d_entry_offsets;
     uint32_t* d_entry_ids;
     void* d_cand;
@@ -375,7 +377,7 @@ struct TannSearcher {
 
 static void FreeSearcher(TannSearcher* s) {
     if (!s) return;
-    cudaFree(s->d_queries); cudaFree(s->d_queries_f32); cudaFree(s->d_entry_offsets);
+    cudaFree(s->d_queries); cudaFree(s->d_queries_f32); cudaFree(s->d_queries_u8); cudaFree(s->d_not_u8); cudaFree(s->d_entry_offsets);
     cudaFree(s->d_entry_ids); cudaFree(s->d_cand); cudaFree(s->d_cand_refined); cudaFree(s->d_stats);
     cudaFree(s->d_lut2); cudaFree(s->d_dists); cudaFree(s->d_ids); cudaFree(s->d_topk_dists);
     cudaFree(s->d_topk_ids); cudaFree(s->d_counts);
@@ -408,6 +410,8 @@ TannStatus tann_searcher_create(const TannIndexView* index, uint64_t max_queries
     auto host = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaHostAlloc(p, bytes ? bytes : 16, cudaHostAllocDefault); };
     dev(&s->d_queries, Q * d * 4);
     dev((void**)&s->d_queries_f32, Q * d * 4);
+    dev((void**)&s->d_queries_u8, Q * d);
+    dev((void**)&s->d_not_u8, 16);
     dev((void**)&s->d_entry_offsets, (Q + 1) * 4);
     dev((void**)&s->d_entry_ids, Q * max_entries_per_query * 4);
     dev(&s->d_cand, Q * s->max_capacity * 8);
@@ -525,9 +529,18 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         capacity = lr;
         err = p2.error_bounds;
     }
-    st = tann_rerank_exact(&s->ix, rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
-                           s->d_ids, nullptr, nullptr, stream);
-    if (st != TANN_OK) return st;
+    if (query_kind == TANN_KIND_FLOAT32 && s->ix.vector_kind == TANN_KIND_UINT8 && !rerank->use_bound_filter) {
+        // integer-valued float queries (the usual case for uint8 data) can use the integer distance path
+        TANN_CUDA(tann::LaunchF32ToU8Checked(static_cast<const float*>(queries_dev), Q * d, s->d_queries_u8,
+                                             s->d_not_u8, stream));
+        if (rerank->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
+        TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
+                                     s->d_ids, nullptr, stream, s->d_queries_u8, s->d_not_u8));
+    } else {
+        st = tann_rerank_exact(&s->ix, rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
+                               s->d_ids, nullptr, nullptr, stream);
+        if (st != TANN_OK) return st;
+    }
     st = tann_topk_pack(s->d_dists, s->d_ids, Q, rerank->top_n, rerank->top_k, s->d_topk_dists,
                         s->d_topk_ids, stream);
     if (st != TANN_OK) return st;

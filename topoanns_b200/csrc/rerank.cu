@@ -29,31 +29,6 @@ __device__ __forceinline__ const uint8_t* VectorPtr(const TannIndexView& ix, uin
     return base + (local / ix.vectors_per_page) * ix.page_bytes + (local % ix.vectors_per_page) * ix.vector_bytes;
 }
 
-// Float path, any pair of kinds. Result valid in lane 0.
-__device__ __forceinline__ float ExactFloat(const void* q, uint32_t qkind, const void* v, uint32_t vkind,
-                                            uint32_t dim, uint32_t lane) {
-    float acc = 0.0f;
-    for (uint32_t i = lane; i < dim; i += 32) {
-        const float diff = LoadAsFloat<float>(v, vkind, i) - LoadAsFloat<float>(q, qkind, i);
-        acc = fmaf(diff, diff, acc);
-    }
-    return WarpTreeSum(acc);
-}
-
-// Integer path: dim % 4 == 0, both rows 4-byte aligned. Result valid in every lane.
-__device__ __forceinline__ float ExactU8(const uint8_t* q, const uint8_t* v, uint32_t dim, uint32_t lane) {
-    const uint32_t* q4 = reinterpret_cast<const uint32_t*>(q);
-    const uint32_t* v4 = reinterpret_cast<const uint32_t*>(v);
-    uint32_t acc = 0;
-    for (uint32_t i = lane; i < dim / 4; i += 32) {
-        const uint32_t ad = __vabsdiffu4(__ldg(v4 + i), q4[i]);
-        acc = __dp4a(ad, ad, acc);
-    }
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) acc += __shfl_xor_sync(kFull, acc, off);
-    return static_cast<float>(acc);
-}
-
 __device__ __forceinline__ float LowerBoundSq(float approx_sq, float err) {
     const float a = sqrtf(fmaxf(approx_sq, 0.0f));
     const float lo = fmaxf(0.0f, a - err);
@@ -64,7 +39,8 @@ __global__ void __launch_bounds__(kRerankThreads)
 rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, const Cand* __restrict__ cand,
               uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
               const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
-              uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts) {
+              uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts,
+              const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag) {
     extern __shared__ __align__(16) unsigned char rr_smem[];
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(rr_smem);   // [padded]
     uint8_t* qrow = reinterpret_cast<uint8_t*>(keys + padded);                   // query row copy
@@ -72,9 +48,14 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
     __shared__ unsigned int s_exact, s_filtered;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t dim = ix.dim;
+    // Float queries whose values are all integers in [0, 255] (checked on the device by the caller,
+    // which then passes their uint8 copy) take the integer path too: same bits, 4 bytes per load.
+    const bool as_u8 = qkind == TANN_KIND_UINT8 || (queries_u8 != nullptr && not_u8_flag != nullptr && *not_u8_flag == 0u);
+    const bool int_path = as_u8 && ix.vector_kind == TANN_KIND_UINT8 && (dim % 4 == 0) && dim <= 256 &&
+                          (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0);
+    const bool swap_queries = int_path && qkind != TANN_KIND_UINT8;
+    if (swap_queries) { queries = queries_u8; qkind = TANN_KIND_UINT8; }
     const uint32_t qbytes = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
-    const bool int_path = qkind == TANN_KIND_UINT8 && ix.vector_kind == TANN_KIND_UINT8 &&
-                          (dim % 4 == 0) && dim <= 256 && (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0);
     const uint32_t tile = p.tile == 0 ? p.top_n : p.tile;
     unsigned long long tot_exact = 0, tot_filtered = 0;
 
@@ -99,25 +80,86 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
         for (uint32_t rb = 0; rb < p.top_n; rb += tile) {
             const uint32_t rc = min(tile, p.top_n - rb);
             const float threshold = s_threshold;
-            for (uint32_t r = rb + warp; r < rb + rc; r += kRerankThreads / 32) {
-                if (r >= capacity) continue;
-                const Cand c = cand[q * capacity + r];
-                if (c.id == kInvalid) continue;
-                const uint32_t id = c.id & kRawMask;
-                if (id >= ix.num_nodes) continue;
-                if (p.use_bound_filter && isfinite(threshold)) {
-                    if (LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id)) > threshold) {
-                        if (lane == 0) atomicAdd(&s_filtered, 1u);
-                        continue;
+            // A warp scores kGroup candidates per step: all their row loads are issued before any
+            // reduction, so several random 128-byte (or longer) reads are in flight per lane.
+            constexpr uint32_t kGroup = 4;
+            for (uint32_t r0 = rb + warp * kGroup; r0 < rb + rc; r0 += (kRerankThreads / 32) * kGroup) {
+                const uint8_t* vptr[kGroup];
+                uint32_t ids[kGroup];
+                bool act[kGroup];
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g) {
+                    const uint32_t r = r0 + g;
+                    act[g] = false;
+                    ids[g] = kInvalid;
+                    vptr[g] = nullptr;
+                    if (r >= rb + rc || r >= capacity) continue;
+                    const Cand c = cand[q * capacity + r];
+                    if (c.id == kInvalid) continue;
+                    const uint32_t id = c.id & kRawMask;
+                    if (id >= ix.num_nodes) continue;
+                    if (p.use_bound_filter && isfinite(threshold)) {
+                        if (LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id)) > threshold) {
+                            if (lane == 0) atomicAdd(&s_filtered, 1u);
+                            continue;
+                        }
                     }
+                    act[g] = true;
+                    ids[g] = id;
+                    vptr[g] = VectorPtr(ix, id);
                 }
-                const uint8_t* v = VectorPtr(ix, id);
-                float dist;
-                if (int_path) dist = ExactU8(qrow, v, dim, lane);
-                else dist = ExactFloat(qrow, qkind, v, ix.vector_kind, dim, lane);
+                float dist[kGroup];
+                if (int_path) {
+                    uint32_t acc[kGroup];
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0;
+                    const uint32_t* q4 = reinterpret_cast<const uint32_t*>(qrow);
+                    for (uint32_t i = lane; i < dim / 4; i += 32) {
+                        uint32_t w[kGroup];
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g)
+                            w[g] = act[g] ? __ldg(reinterpret_cast<const uint32_t*>(vptr[g]) + i) : 0u;
+                        const uint32_t qw = q4[i];
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g) {
+                            const uint32_t ad = __vabsdiffu4(w[g], qw);
+                            acc[g] = __dp4a(ad, ad, acc[g]);
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) {
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) acc[g] += __shfl_xor_sync(kFull, acc[g], off);
+                        dist[g] = static_cast<float>(acc[g]);
+                    }
+                } else {
+                    float acc[kGroup];
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0.0f;
+                    for (uint32_t i = lane; i < dim; i += 32) {
+                        float v[kGroup];
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g)
+                            v[g] = act[g] ? LoadAsFloat<float>(vptr[g], ix.vector_kind, i) : 0.0f;
+                        const float qv = LoadAsFloat<float>(qrow, qkind, i);
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g) {
+                            const float diff = v[g] - qv;
+                            acc[g] = fmaf(diff, diff, acc[g]);
+                        }
+                    }
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) dist[g] = WarpTreeSum(acc[g]);
+                }
                 if (lane == 0) {
-                    keys[r] = KeyOf(dist, id);
-                    atomicAdd(&s_exact, 1u);
+                    uint32_t n = 0;
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) {
+                        if (!act[g]) continue;
+                        keys[r0 + g] = KeyOf(dist[g], ids[g]);
+                        ++n;
+                    }
+                    if (n) atomicAdd(&s_exact, n);
                 }
             }
             __syncthreads();
@@ -183,7 +225,8 @@ __global__ void topk_pack_kernel(const float* __restrict__ dists, const uint32_t
 cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, const void* cand,
                          uint32_t capacity, uint64_t Q, const void* queries, uint32_t query_kind,
                          const float* error_bounds, float* out_dists, uint32_t* out_ids,
-                         unsigned long long* out_counts, cudaStream_t stream) {
+                         unsigned long long* out_counts, cudaStream_t stream, const uint8_t* queries_u8,
+                         const uint32_t* not_u8_flag) {
     if (Q == 0 || p.top_n == 0) return cudaSuccess;
     uint32_t padded = 1;
     while (padded < p.top_n) padded <<= 1;
@@ -197,7 +240,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     const uint64_t cap = (uint64_t)SmCount() * 8;
     rerank_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, static_cast<const Cand*>(cand), capacity, Q, queries, query_kind, error_bounds, padded,
-        out_dists, out_ids, out_counts);
+        out_dists, out_ids, out_counts, queries_u8, not_u8_flag);
     return cudaGetLastError();
 }
 
@@ -209,6 +252,33 @@ cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, 
     const uint64_t cap = (uint64_t)SmCount() * 16;
     topk_pack_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, stream>>>(
         dists, ids, Q, top_n, top_k, out_dists, out_ids);
+    return cudaGetLastError();
+}
+
+}  // namespace tann
+
+namespace tann {
+
+// float -> uint8 copy of a query batch; *not_u8_flag becomes non-zero if any value is not an
+// integer in [0, 255] (the flag must be zero on entry).
+__global__ void f32_to_u8_checked_kernel(const float* __restrict__ src, uint64_t n, uint8_t* __restrict__ dst,
+                                         uint32_t* __restrict__ not_u8_flag) {
+    bool bad = false;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+        const float v = src[i];
+        const bool ok = v >= 0.0f && v <= 255.0f && v == truncf(v);
+        bad |= !ok;
+        dst[i] = ok ? (uint8_t)v : 0;
+    }
+    if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(not_u8_flag, 1u);
+}
+
+cudaError_t LaunchF32ToU8Checked(const float* src, uint64_t n, uint8_t* dst, uint32_t* not_u8_flag, cudaStream_t stream) {
+    cudaError_t e = cudaMemsetAsync(not_u8_flag, 0, sizeof(uint32_t), stream);
+    if (e != cudaSuccess || n == 0) return e;
+    const uint64_t blocks = (n + 255) / 256;
+    const uint64_t cap = (uint64_t)SmCount() * 8;
+    f32_to_u8_checked_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, stream>>>(src, n, dst, not_u8_flag);
     return cudaGetLastError();
 }
 

@@ -42,7 +42,10 @@ cudaError_t LaunchCrossTerms(uint32_t dim, uint32_t M, const uint32_t* chunk_off
 cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, const void* cand,
                          uint32_t capacity, uint64_t Q, const void* queries, uint32_t query_kind,
                          const float* error_bounds, float* out_dists, uint32_t* out_ids,
-                         unsigned long long* out_counts, cudaStream_t stream);
+                         unsigned long long* out_counts, cudaStream_t stream,
+                         const uint8_t* queries_u8 = nullptr, const uint32_t* not_u8_flag = nullptr);
+cudaError_t LaunchF32ToU8Checked(const float* src, uint64_t n, uint8_t* dst, uint32_t* not_u8_flag,
+                                 cudaStream_t stream);
 cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, uint32_t top_n,
                            uint32_t top_k, float* out_dists, uint32_t* out_ids, cudaStream_t stream);
 

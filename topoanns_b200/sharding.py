@@ -101,3 +101,47 @@ def _tensor_from_ptr(ptr: int, nbytes: int) -> torch.Tensor:
         __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
     return torch.as_tensor(_Holder(), device="cuda")
+
+
+def pages_from_rows(rows: torch.Tensor, page_bytes: int = 4096) -> torch.Tensor:
+    """[n, d] device tensor -> flat uint8 page array in the vector-store page layout."""
+    n = rows.shape[0]
+    raw = rows.contiguous().view(torch.uint8).view(n, -1)
+    vb = raw.shape[1]
+    vpp = page_bytes // vb
+    pages = torch.zeros(((n + vpp - 1) // vpp, page_bytes), dtype=torch.uint8, device=rows.device)
+    full = (n // vpp) * vpp
+    if full:
+        pages[: n // vpp, : vpp * vb] = raw[:full].view(n // vpp, vpp * vb)
+    if n > full:
+        pages[n // vpp, : (n - full) * vb] = raw[full:].reshape(-1)
+    return pages.view(-1)
+
+
+def peer_index_from_sharded(sh):
+    """Put this rank's shard of a synth_sharded.ShardedSynth into IPC-shared device buffers and return a
+    search.DeviceIndex whose adjacency / code / vector rows resolve to local or peer memory.
+    Returns (index, buffers); keep `buffers` alive and close() them after the last search."""
+    from . import search
+    dev = sh.vectors.device
+    vec_pages = pages_from_rows(sh.vectors)
+    parts = {"adjacency": sh.adjacency.contiguous().view(torch.uint8).view(-1),
+             "codes": sh.pq_codes.contiguous().view(-1), "vectors": vec_pages}
+    buffers, bases = {}, {}
+    for name, t in parts.items():
+        pb = PeerBuffers(t.numel())
+        pb.local_tensor(t.numel()).copy_(t)
+        buffers[name] = pb
+        bases[name] = pb.bases
+    torch.cuda.synchronize()
+    dist.barrier()
+    vb = sh.vectors.shape[1] * sh.vectors.element_size()
+    ix = search.DeviceIndex(
+        num_nodes=sh.total_nodes, degree=sh.adjacency.shape[1], dim=sh.vectors.shape[1],
+        vector_kind=search.kind_of(sh.vectors), pq_tables_col_major=sh.pq_tables.t().contiguous(),
+        pq_centroid=sh.pq_centroid.contiguous(), pq_chunk_offsets=sh.pq_chunk_offsets.to(torch.int32).contiguous(),
+        vector_bytes=vb, vectors_per_page=4096 // vb, page_bytes=4096, adjacency_bases=bases["adjacency"],
+        codes_bases=bases["codes"], vector_bases=bases["vectors"], rows_per_shard=sh.rows_per_shard,
+        keepalive=[buffers])
+    _ = dev
+    return ix, buffers
