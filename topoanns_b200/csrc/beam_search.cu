@@ -22,6 +22,21 @@
 #include "beam_args.h"
 #include "tann_launch.h"
 
+// Optional per-phase cycle counters (development builds only: -DTANN_BEAM_PROFILE). Thread 0 adds
+// clock64() deltas per phase into a [Q][8] uint64 array passed through BeamArgs::status.
+#ifdef TANN_BEAM_PROFILE
+#define TANN_PHASE(i)                                            \
+    do {                                                         \
+        if (tid == 0) {                                          \
+            const long long now__ = clock64();                   \
+            prof_acc[i] += (unsigned long long)(now__ - prof_t); \
+            prof_t = now__;                                      \
+        }                                                        \
+    } while (0)
+#else
+#define TANN_PHASE(i) do {} while (0)
+#endif
+
 namespace tann {
 
 constexpr int kBeamThreads = 128;
@@ -244,6 +259,10 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
     const uint32_t lane = tid & 31;
 
     for (uint64_t q = blockIdx.x; q < a.num_queries; q += gridDim.x) {
+#ifdef TANN_BEAM_PROFILE
+        unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        long long prof_t = clock64();
+#endif
         // ---- per-query set-up --------------------------------------------------------------
         if (a.lut != nullptr) {
             const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
@@ -288,6 +307,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         if (tid < 32) ctl.ls_prev_ids[tid] = kInvalid;
         __syncthreads();
 
+        TANN_PHASE(0);  // 0: set-up (table build, clears)
         // block-uniform state, identical in every thread
         uint32_t valid = 0, visited = 0, hash_iter = 0;
         unsigned long long* cur = cand_a;
@@ -386,6 +406,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (ctl.stop) break;
                 nslots = ctl.nsel * deg;
             }
+            TANN_PHASE(1);  // 1: stop tests + selection
 
             // ---- phase 1: gather slot ids, Bloom tests ----------------------------------------
             unsigned long long my_key = kInvalidKey;  // kSingle: this thread's slot
@@ -427,6 +448,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 }
             }
             if (kSingle) __syncthreads();  // every test of the round precedes every add
+            TANN_PHASE(2);  // 2: slot ids (adjacency / entries) + Bloom tests
             // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
             uint32_t fv = 0;
             for (uint32_t r = 0; r < rounds; ++r) {
@@ -444,6 +466,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 fv += __syncthreads_count(pass);
             }
             const uint32_t nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
+            TANN_PHASE(3);  // 3: Bloom adds + code rows + table sums
 
             // ---- order the frontier -----------------------------------------------------------
             // sorted[0 .. n) = the frontier entries that can still enter the list, ascending.
@@ -482,6 +505,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 n = fv;
             }
 
+            TANN_PHASE(4);  // 4: filter + compaction + rank sort
             // ---- merge (:1338-1424) as a parallel merge-path --------------------------------------
             uint32_t accepted = 0;
             {
@@ -533,6 +557,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             if (tid == 0 && ctl.first_full == 0xffffffffu && nv >= L)
                 ctl.first_full = in_entries ? 0u : ctl.iterations;
             __syncthreads();
+            TANN_PHASE(5);  // 5: acceptance + merge
             // ---- prefix state (:822-845): unexpanded bitmap, Bloom rebuild every third merge ----
             const uint32_t prefix = min(nv, L);
             for (uint32_t base = 0; base < UW * 32; base += kBeamThreads) {
@@ -549,6 +574,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (lane == 0 && (i >> 5) < UW) unexp[i >> 5] = word;
             }
             __syncthreads();
+            TANN_PHASE(6);  // 6: bitmap + Bloom rebuild
 
             if (in_entries) {
                 ++batch;
@@ -571,6 +597,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             st[4] = valid; st[5] = ctl.first_full; st[6] = 0; st[7] = 0;
         }
         __syncthreads();
+        TANN_PHASE(7);  // 7: output
+#ifdef TANN_BEAM_PROFILE
+        if (tid == 0 && a.status != nullptr) {
+            unsigned long long* o = reinterpret_cast<unsigned long long*>(a.status) + q * 8;
+            for (int i = 0; i < 8; ++i) o[i] = prof_acc[i];
+        }
+#endif
     }
 }
 
