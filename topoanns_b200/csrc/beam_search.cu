@@ -45,9 +45,8 @@ constexpr int kBeamThreads = 128;
 // Counters every thread can derive identically (valid, visited, merges since the last Bloom
 // rebuild) are kept in registers instead.
 struct BeamCtl {
-    uint32_t expanded, iterations, first_full;
-    uint32_t nsel, stop;
-    uint32_t selected[TANN_MAX_SEARCH_WIDTH];
+    uint32_t first_full;
+    uint32_t nsel, stop, stop_scan;
     // learned stop state (:2252-2258)
     uint32_t ls_stage, ls_has_prev, ls_topk_changed;
     float ls_prev_dk, ls_prev_boundary;
@@ -78,13 +77,25 @@ __device__ __forceinline__ uint32_t FindFirstSetBit(const uint32_t* bits, uint32
     return limit;
 }
 
+// Sets the expanded flag of the list elements this lane picked (the picks sel_begin..sel_end-1 are
+// the lowest set bits of its bitmap word). Runs on warp 0 once every warp has read the ids.
+__device__ __forceinline__ void MarkExpanded(unsigned long long* cur, uint32_t word, uint32_t sel_begin,
+                                             uint32_t sel_end, uint32_t lane) {
+    for (uint32_t sidx = sel_begin; sidx < sel_end; ++sidx) {
+        const uint32_t bit = __ffs(word) - 1;
+        word &= word - 1u;
+        cur[lane * 32 + bit] |= kExpandedBit;
+    }
+}
+
 // Learned stop on one thread; returns true when the traversal has to stop.
 __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t valid, uint32_t visited,
-                            const unsigned long long* cand, const uint32_t* unexp, uint32_t top_l) {
+                            uint32_t expanded, const unsigned long long* cand, const uint32_t* unexp,
+                            uint32_t top_l) {
     while (s.ls_stage < ls.num_stages) {
         const uint32_t p = ls.stage_prefixes[s.ls_stage];
         if (p == 0 || p >= top_l || p < ls.top_k) { ++s.ls_stage; continue; }
-        if (valid < top_l || valid < p || valid < ls.top_k || s.expanded < p) break;
+        if (valid < top_l || valid < p || valid < ls.top_k || expanded < p) break;
         const float dk = KeyDist(cand[ls.top_k - 1]);
         const float boundary = KeyDist(cand[p - 1]);
         const uint32_t next64_end = min(p + 64u, top_l);
@@ -95,7 +106,7 @@ __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t vali
         const bool has_prev = s.ls_has_prev != 0;
         float f[TANN_STOP_FEATURES];
         f[0] = ls.feature_mask[0] ? (float)p * ls.inv_top_l : 0.0f;
-        f[1] = ls.feature_mask[1] ? (float)s.expanded * ls.inv_top_l : 0.0f;
+        f[1] = ls.feature_mask[1] ? (float)expanded * ls.inv_top_l : 0.0f;
         f[2] = ls.feature_mask[2] ? (float)visited * ls.inv_top_l : 0.0f;
         const bool need_best = ls.feature_mask[3] || (ls.feature_mask[4] && ls.next64_flag_mode);
         uint32_t best = top_l;
@@ -153,42 +164,55 @@ __device__ bool LearnedStop(const TannLearnedStop& ls, BeamCtl& s, uint32_t vali
     return false;
 }
 
+// The code row of a node as 32-bit words (specialised chunk counts only): loading is split from
+// summing so that the loads can be issued before a barrier and consumed after it.
+template <int kM>
+__device__ __forceinline__ void LoadCodeWords(const uint8_t* row, uint32_t (&w)[kM > 0 ? kM / 4 : 1]) {
+    const uint4* r4 = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+    for (int i = 0; i < kM / 16; ++i) {
+        const uint4 v = __ldg(r4 + i);
+        w[4 * i + 0] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+    }
+}
+
 // ADC distance of one node by one thread, in the reference's order: per group of 32 chunks the
 // 16/8/4/2/1 tree over "lanes", groups added in order. Terms beyond M are exact zeros in the
 // reference and are simply left out here.
 template <int kM>
+__device__ __forceinline__ float AdcFromWords(const float* lut, const uint32_t (&w)[kM > 0 ? kM / 4 : 1]) {
+    static_assert(kM > 0 && kM % 16 == 0, "specialised chunk counts are multiples of 16");
+    float total = 0.0f;
+#pragma unroll
+    for (int base = 0; base < kM; base += 32) {
+        const int n = (kM - base) < 32 ? (kM - base) : 32;
+        float x[32];
+#pragma unroll
+        for (int l = 0; l < 32; ++l) {
+            if (l < n) {
+                const int c = base + l;
+                const uint32_t code = (w[c >> 2] >> ((c & 3) * 8)) & 0xffu;
+                x[l] = lut[c * kCentroids + code];
+            }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+            for (int i = 0; i < off; ++i)
+                if (i + off < n) x[i] = x[i] + x[i + off];
+        }
+        total = (base == 0) ? x[0] : total + x[0];
+    }
+    return total;
+}
+
+template <int kM>
 __device__ __forceinline__ float AdcTreeThread(const float* lut, const uint8_t* row, uint32_t M) {
     float total = 0.0f;
     if constexpr (kM > 0) {
-        static_assert(kM % 16 == 0, "specialised chunk counts are multiples of 16");
         uint32_t w[kM / 4];
-        const uint4* r4 = reinterpret_cast<const uint4*>(row);
-#pragma unroll
-        for (int i = 0; i < kM / 16; ++i) {
-            const uint4 v = __ldg(r4 + i);
-            w[4 * i + 0] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
-        }
-#pragma unroll
-        for (int base = 0; base < kM; base += 32) {
-            constexpr int kDummy = 0; (void)kDummy;
-            const int n = (kM - base) < 32 ? (kM - base) : 32;
-            float x[32];
-#pragma unroll
-            for (int l = 0; l < 32; ++l) {
-                if (l < n) {
-                    const int c = base + l;
-                    const uint32_t code = (w[c >> 2] >> ((c & 3) * 8)) & 0xffu;
-                    x[l] = lut[c * kCentroids + code];
-                }
-            }
-#pragma unroll
-            for (int off = 16; off >= 1; off >>= 1) {
-#pragma unroll
-                for (int i = 0; i < off; ++i)
-                    if (i + off < n) x[i] = x[i] + x[i + off];
-            }
-            total = (base == 0) ? x[0] : total + x[0];
-        }
+        LoadCodeWords<kM>(row, w);
+        total = AdcFromWords<kM>(lut, w);
     } else {
         for (uint32_t base = 0; base < M; base += 32) {
             const uint32_t n = min(32u, M - base);
@@ -207,6 +231,66 @@ __device__ __forceinline__ float AdcTreeThread(const float* lut, const uint8_t* 
         }
     }
     return total;
+}
+
+// Query look-up table (src/search/pq_query_tables.cu:33-52), four consecutive centroids per thread
+// and step: one 16-byte load per dim and the same per-entry FMA chain (ascending dim) as the
+// one-entry form. kSub = dims per chunk when every chunk has that many: the loads of a step
+// (about eight per thread) are then all issued before the first is used, which is what keeps the
+// 128 KB table stream from L2 from being latency-bound.
+template <int kSub>
+__device__ __forceinline__ void BuildLutUniform(float* lut, const float* sq, const float* tables,
+                                                uint32_t M, uint32_t tid) {
+    constexpr int kItems = kSub <= 2 ? 4 : (kSub <= 4 ? 2 : 1);
+    const uint32_t total = M * (kCentroids / 4);
+    for (uint32_t item0 = tid; item0 < total; item0 += kBeamThreads * kItems) {
+        float4 t[kItems][kSub];
+#pragma unroll
+        for (int u = 0; u < kItems; ++u) {
+            const uint32_t item = item0 + u * kBeamThreads;
+            if (item < total) {
+                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+#pragma unroll
+                for (int sd = 0; sd < kSub; ++sd)
+                    t[u][sd] = __ldg(reinterpret_cast<const float4*>(
+                        tables + (size_t)(m * kSub + sd) * kCentroids + c4));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItems; ++u) {
+            const uint32_t item = item0 + u * kBeamThreads;
+            if (item < total) {
+                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int sd = 0; sd < kSub; ++sd) {
+                    const float sv = sq[m * kSub + sd];
+                    float df = t[u][sd].x - sv; acc.x = fmaf(df, df, acc.x);
+                    df = t[u][sd].y - sv; acc.y = fmaf(df, df, acc.y);
+                    df = t[u][sd].z - sv; acc.z = fmaf(df, df, acc.z);
+                    df = t[u][sd].w - sv; acc.w = fmaf(df, df, acc.w);
+                }
+                *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
+            }
+        }
+    }
+}
+
+__device__ __noinline__ void BuildLutGeneric(float* lut, const float* sq, const uint32_t* offs,
+                                             const float* tables, uint32_t M, uint32_t tid) {
+    for (uint32_t item = tid; item < M * (kCentroids / 4); item += kBeamThreads) {
+        const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(tables + (size_t)dim * kCentroids + c4));
+            const float sv = sq[dim];
+            float df = t.x - sv; acc.x = fmaf(df, df, acc.x);
+            df = t.y - sv; acc.y = fmaf(df, df, acc.y);
+            df = t.z - sv; acc.z = fmaf(df, df, acc.z);
+            df = t.w - sv; acc.w = fmaf(df, df, acc.w);
+        }
+        *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
+    }
 }
 
 // Bitonic sort of F keys held in shared memory (any power of two F).
@@ -255,8 +339,19 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
     __shared__ BeamCtl ctl;
     __shared__ uint32_t s_surv;
+    __shared__ uint32_t s_sel[kBeamThreads / 32][TANN_MAX_SEARCH_WIDTH];  // selected nodes, one copy per warp
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31;
+
+    // Chunks of equal width (the usual case) take the unrolled table build.
+    uint32_t uniform_sub = 0;
+    if (a.lut == nullptr) {
+        const uint32_t sub0 = __ldg(a.ix.pq_chunk_offsets + 1) - __ldg(a.ix.pq_chunk_offsets);
+        bool same = __ldg(a.ix.pq_chunk_offsets) == 0u;
+        for (uint32_t i = tid; i < M; i += kBeamThreads)
+            same = same && (__ldg(a.ix.pq_chunk_offsets + i + 1) - __ldg(a.ix.pq_chunk_offsets + i)) == sub0;
+        uniform_sub = __syncthreads_and(same) ? sub0 : 0u;
+    }
 
     for (uint64_t q = blockIdx.x; q < a.num_queries; q += gridDim.x) {
 #ifdef TANN_BEAM_PROFILE
@@ -267,7 +362,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         if (a.lut != nullptr) {
             const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
             float4* dst = reinterpret_cast<float4*>(lut);
-#pragma unroll 4
+#pragma unroll 8
             for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
         } else {
             // src/search/pq_query_tables.cu:33-52
@@ -275,28 +370,21 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 sq[i] = LoadAsFloat<float>(a.queries, a.query_kind, q * d + i) - __ldg(a.ix.pq_centroid + i);
             for (uint32_t i = tid; i <= M; i += kBeamThreads) offs[i] = __ldg(a.ix.pq_chunk_offsets + i);
             __syncthreads();
-            // Four consecutive centroids per thread and step: one 16-byte load per dim, the same
-            // per-entry FMA chain (ascending dim) as the one-entry form.
-#pragma unroll 4
-            for (uint32_t item = tid; item < M * (kCentroids / 4); item += kBeamThreads) {
-                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
-                    const float4 t = __ldg(reinterpret_cast<const float4*>(a.ix.pq_tables_col_major + (size_t)dim * kCentroids + c4));
-                    const float sv = sq[dim];
-                    float df = t.x - sv; acc.x = fmaf(df, df, acc.x);
-                    df = t.y - sv; acc.y = fmaf(df, df, acc.y);
-                    df = t.z - sv; acc.z = fmaf(df, df, acc.z);
-                    df = t.w - sv; acc.w = fmaf(df, df, acc.w);
-                }
-                *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
+            switch (uniform_sub) {
+                case 1: BuildLutUniform<1>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 2: BuildLutUniform<2>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 3: BuildLutUniform<3>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 4: BuildLutUniform<4>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 6: BuildLutUniform<6>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 8: BuildLutUniform<8>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                default: BuildLutGeneric(lut, sq, offs, a.ix.pq_tables_col_major, M, tid); break;
             }
         }
-        for (uint32_t i = tid; i < C; i += kBeamThreads) { cand_a[i] = kInvalidKey; cand_b[i] = kInvalidKey; }
+        // cand_b needs no clear: a merge writes all C elements of the buffer it fills.
+        for (uint32_t i = tid; i < C; i += kBeamThreads) cand_a[i] = kInvalidKey;
         for (uint32_t i = tid; i < kBloomWords; i += kBeamThreads) bloom[i] = 0u;
         for (uint32_t i = tid; i < UW; i += kBeamThreads) unexp[i] = 0u;
         if (tid == 0) {
-            ctl.expanded = ctl.iterations = 0;
             ctl.first_full = 0xffffffffu;
             ctl.nsel = 0; ctl.stop = 0;
             ctl.ls_stage = 0; ctl.ls_has_prev = 0; ctl.ls_topk_changed = 0;
@@ -309,7 +397,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
         TANN_PHASE(0);  // 0: set-up (table build, clears)
         // block-uniform state, identical in every thread
-        uint32_t valid = 0, visited = 0, hash_iter = 0;
+        uint32_t valid = 0, visited = 0, hash_iter = 0, expanded = 0, iterations = 0;
         unsigned long long* cur = cand_a;
         unsigned long long* nxt = cand_b;
         const uint32_t entry_begin = a.entry_offsets[q];
@@ -321,99 +409,113 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         // ---- one pass per batch of slot ids: entry batches first, then expansions ----------
         while (true) {
             uint32_t nslots;
+            uint32_t sel_word = 0, sel_begin = 0, sel_end = 0;  // this lane's share of the selection
             if (in_entries) {
                 nslots = slots;
             } else {
-                // stop tests and selection by warp 0 (:2414-2513). The unexpanded bitmap was rebuilt
-                // from the list after the last merge, so every set bit is a valid, unexpanded rank
-                // below min(valid, L): the first W set bits are exactly what the reference's serial
-                // scan picks, and they can be found with one popcount scan over the words.
-                if (tid < 32) {
-                    uint32_t stop = 0, nsel = 0;
-                    if (lane == 0) {
-                        if (ctl.expanded >= a.p.max_expansions || valid == 0) stop = 1;
-                        else if (a.p.learned_stop.enabled &&
-                                 LearnedStop(a.p.learned_stop, ctl, valid, visited, cur, unexp, L)) stop = 1;
-                    }
-                    stop = __shfl_sync(kFull, stop, 0);
-                    if (!stop) {
-                        const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
-                        bool any = false;
+                // Stop tests and selection (:2414-2513). The unexpanded bitmap was rebuilt from the
+                // list after the last merge, so every set bit is a valid, unexpanded rank below
+                // min(valid, L): the first W set bits are exactly what the reference's serial scan
+                // picks. Every warp finds them by itself with one popcount scan over the words (all
+                // inputs are block-uniform), so no barrier separates the bitmap from the adjacency
+                // loads; warp 0 marks the picked elements as expanded after the next barrier.
+                uint32_t stop = 0, nsel = 0;
+                if (expanded >= a.p.max_expansions || valid == 0) {
+                    stop = 2;
+                } else if (a.p.learned_stop.enabled) {
+                    if (tid == 0)
+                        ctl.stop = LearnedStop(a.p.learned_stop, ctl, valid, visited, expanded, cur, unexp, L) ? 2u : 0u;
+                    __syncthreads();
+                    stop = ctl.stop;
+                }
+                if (!stop) {
+                    const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
+                    if (UW <= 32) {
+                        sel_word = lane < UW ? unexp[lane] : 0u;
+                        bool any;
                         if (prefix_stop && a.p.stop_use_expanded) {
-                            any = !(valid >= L && ctl.expanded >= a.p.stop_prefix);
+                            any = !(valid >= L && expanded >= a.p.stop_prefix);
                         } else {
                             const uint32_t words = (prefix_stop && valid >= a.p.stop_prefix)
                                                        ? (a.p.stop_prefix + 31) / 32 : UW;
-                            bool mine = false;
-                            for (uint32_t w = lane; w < words; w += 32) mine |= unexp[w] != 0u;
-                            any = __ballot_sync(kFull, mine) != 0u;
+                            any = __ballot_sync(kFull, lane < words && sel_word != 0u) != 0u;
                         }
                         if (!any) {
-                            stop = 1;
-                        } else if (UW <= 32) {
-                            const uint32_t word = lane < UW ? unexp[lane] : 0u;
-                            const uint32_t cnt = __popc(word);
+                            stop = 2;
+                        } else {
+                            const uint32_t cnt = __popc(sel_word);
                             uint32_t incl = cnt;
 #pragma unroll
                             for (int off = 1; off < 32; off <<= 1) {
                                 const uint32_t t = __shfl_up_sync(kFull, incl, off);
                                 if (lane >= (uint32_t)off) incl += t;
                             }
-                            const uint32_t excl = incl - cnt;
                             nsel = min(__shfl_sync(kFull, incl, 31), W);
-                            uint32_t w = word;
-                            for (uint32_t sidx = excl; sidx < min(incl, nsel); ++sidx) {
+                            sel_begin = incl - cnt;
+                            sel_end = min(incl, nsel);
+                            uint32_t w = sel_word;
+                            for (uint32_t sidx = sel_begin; sidx < sel_end; ++sidx) {
                                 const uint32_t bit = __ffs(w) - 1;
                                 w &= w - 1u;
-                                const uint32_t idx = lane * 32 + bit;
-                                const unsigned long long k = cur[idx];
-                                cur[idx] = k | kExpandedBit;
-                                ctl.selected[sidx] = KeyPackedId(k) & kRawMask;
+                                s_sel[tid >> 5][sidx] = KeyPackedId(cur[lane * 32 + bit]) & kRawMask;
                             }
-                            if (w != word) unexp[lane] = w;
-                            if (lane == 0) { ++ctl.iterations; ctl.expanded += nsel; }
-                            if (nsel == 0) stop = 1;
-                        } else {
-                            if (lane == 0) {
-                                ++ctl.iterations;
-                                for (uint32_t w = 0; w < UW && nsel < W; ++w) {
-                                    uint32_t word = unexp[w];
-                                    while (word != 0u && nsel < W) {
-                                        const uint32_t bit = __ffs(word) - 1;
-                                        const uint32_t idx = w * 32 + bit;
-                                        word &= word - 1u;
-                                        unexp[w] &= ~(1u << bit);
-                                        if (idx >= C || idx >= L || idx >= valid) continue;
-                                        const unsigned long long k = cur[idx];
-                                        const uint32_t pid = KeyPackedId(k);
-                                        if (pid == kInvalid || (pid & kExpandedBit)) continue;
-                                        cur[idx] = k | kExpandedBit;
-                                        ctl.selected[nsel++] = pid & kRawMask;
-                                        ++ctl.expanded;
-                                    }
-                                }
-                            }
-                            nsel = __shfl_sync(kFull, nsel, 0);
+                            __syncwarp();
                             if (nsel == 0) stop = 1;
                         }
-                    }
-                    if (lane == 0) {
-                        ctl.stop = stop;
-                        ctl.nsel = nsel;
+                    } else {
+                        // more than 1024 list ranks: serial scan by one thread, shared through a barrier
+                        if (tid == 0) {
+                            bool any = false;
+                            if (prefix_stop && a.p.stop_use_expanded) {
+                                any = !(valid >= L && expanded >= a.p.stop_prefix);
+                            } else {
+                                const uint32_t words = (prefix_stop && valid >= a.p.stop_prefix)
+                                                           ? (a.p.stop_prefix + 31) / 32 : UW;
+                                for (uint32_t w = 0; w < words; ++w) any |= unexp[w] != 0u;
+                            }
+                            uint32_t found = 0;
+                            for (uint32_t w = 0; any && w < UW && found < W; ++w) {
+                                uint32_t word = unexp[w];
+                                while (word != 0u && found < W) {
+                                    const uint32_t idx = w * 32 + __ffs(word) - 1;
+                                    word &= word - 1u;
+                                    const unsigned long long k = cur[idx];
+                                    cur[idx] = k | kExpandedBit;
+                                    for (int wp = 0; wp < kBeamThreads / 32; ++wp)
+                                        s_sel[wp][found] = KeyPackedId(k) & kRawMask;
+                                    ++found;
+                                }
+                            }
+                            ctl.nsel = found;
+                            ctl.stop_scan = !any ? 2u : (found == 0 ? 1u : 0u);
+                        }
+                        __syncthreads();
+                        stop = ctl.stop_scan;
+                        nsel = ctl.nsel;
                     }
                 }
-                __syncthreads();
-                if (ctl.stop) break;
-                nslots = ctl.nsel * deg;
+                if (stop) {
+                    // the reference counts an iteration whenever the scan for nodes ran, also when
+                    // it found none (:2479-2513); stop == 2 marks the stops taken before the scan
+                    if (stop == 1) ++iterations;
+                    break;
+                }
+                ++iterations;
+                expanded += nsel;
+                nslots = nsel * deg;
             }
             TANN_PHASE(1);  // 1: stop tests + selection
 
             // ---- phase 1: gather slot ids, Bloom tests ----------------------------------------
             unsigned long long my_key = kInvalidKey;  // kSingle: this thread's slot
+            uint32_t my_words[kM > 0 ? kM / 4 : 1];     // kSingle: its code row
             if (!kSingle)
                 for (uint32_t i = tid; i < F; i += kBeamThreads) fkey[i] = kInvalidKey;
             const uint32_t rounds = kSingle ? 1u : (nslots + kBeamThreads - 1) / kBeamThreads;
-            if (!kSingle) __syncthreads();
+            if (!kSingle) {
+                __syncthreads();
+                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane);
+            }
             for (uint32_t r = 0; r < rounds; ++r) {
                 const uint32_t s = r * kBeamThreads + tid;
                 uint32_t id = kInvalid;
@@ -423,7 +525,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         if (e < num_entries) id = __ldg(a.entry_ids + entry_begin + e);
                     } else {
                         const uint32_t k = s / deg, j = s - k * deg;
-                        const uint32_t node = ctl.selected[k];
+                        const uint32_t node = s_sel[tid >> 5][k];
                         const uint32_t* row =
                             (node < a.ix.adjacency_cached_rows)
                                 ? a.ix.adjacency_cache + (uint64_t)node * deg
@@ -433,6 +535,9 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     }
                 }
                 const bool pass = id != kInvalid && id < N && !BloomTest(id, bloom);
+                // The code row does not depend on the barrier below: request it now.
+                if constexpr (kSingle && kM > 0)
+                    if (pass) LoadCodeWords<kM>(ShardRow(a.ix.codes, id, M), my_words);
                 // Park the surviving id in the key slot; phase 2 turns it into a key.
                 const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
                 if (kSingle) {
@@ -447,7 +552,10 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     __syncthreads();
                 }
             }
-            if (kSingle) __syncthreads();  // every test of the round precedes every add
+            if (kSingle) {
+                __syncthreads();  // every test of the round precedes every add
+                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane);
+            }
             TANN_PHASE(2);  // 2: slot ids (adjacency / entries) + Bloom tests
             // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
             uint32_t fv = 0;
@@ -458,8 +566,12 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (pass) {
                     const uint32_t id = (uint32_t)parked;
                     if (kSingle) BloomAdd(id, bloom);
-                    const uint8_t* row = ShardRow(a.ix.codes, id, M);
-                    const float dist = AdcTreeThread<kM>(lut, row, M);
+                    float dist;
+                    if constexpr (kSingle && kM > 0) {
+                        dist = AdcFromWords<kM>(lut, my_words);
+                    } else {
+                        dist = AdcTreeThread<kM>(lut, ShardRow(a.ix.codes, id, M), M);
+                    }
                     const unsigned long long key = ((unsigned long long)OrderedBits(dist) << 32) | id;
                     if (kSingle) my_key = key; else fkey[s] = key;
                 }
@@ -510,14 +622,16 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             uint32_t accepted = 0;
             {
                 const uint32_t lim = min(n, nv);
-                for (uint32_t base = 0; base < lim; base += kBeamThreads) {
+                uint32_t base = 0;
+                do {
                     const uint32_t x = base + tid;
                     bool pred = false;
                     if (x < lim) pred = sorted[x] < (cur[nv - 1 - x] & kCmpMask);
                     const uint32_t cnt = __syncthreads_count(pred);
                     accepted += cnt;
                     if (cnt < (uint32_t)kBeamThreads) break;  // the predicate is monotone in x
-                }
+                    base += kBeamThreads;
+                } while (base < lim);
             }
             if (accepted != 0) {
                 const uint32_t kept = nv - accepted;
@@ -555,7 +669,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 for (uint32_t i = tid; i < kBloomWords; i += kBeamThreads) bloom[i] = 0u;
             }
             if (tid == 0 && ctl.first_full == 0xffffffffu && nv >= L)
-                ctl.first_full = in_entries ? 0u : ctl.iterations;
+                ctl.first_full = in_entries ? 0u : iterations;
             __syncthreads();
             TANN_PHASE(5);  // 5: acceptance + merge
             // ---- prefix state (:822-845): unexpanded bitmap, Bloom rebuild every third merge ----
@@ -593,7 +707,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         }
         if (tid == 0) {
             uint32_t* st = a.out_stats + q * 8;
-            st[0] = visited; st[1] = ctl.expanded; st[2] = 0; st[3] = ctl.iterations;
+            st[0] = visited; st[1] = expanded; st[2] = 0; st[3] = iterations;
             st[4] = valid; st[5] = ctl.first_full; st[6] = 0; st[7] = 0;
         }
         __syncthreads();

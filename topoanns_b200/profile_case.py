@@ -1,0 +1,72 @@
+"""Run the stages of the search path a few times on a small synthetic index, for use under a profiler
+(`ncu -k regex:beam_search ... python -m topoanns_b200.profile_case --nodes 1000000 --queries 4000`).
+The index is the bench workload's generator at a reduced size: large enough that gathers miss L2, small
+enough that a multi-pass capture saves and restores little device memory. Prints one line per stage
+with its CUDA-event time.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+
+import torch
+
+from . import search, synth
+
+
+def _time(fn, reps):
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    out = None
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        start.record()
+        out = fn()
+        stop.record()
+        torch.cuda.synchronize()
+    return out, start.elapsed_time(stop)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--config", default="cfg2", choices=sorted(synth.CONFIGS))
+    ap.add_argument("--nodes", type=int, default=1_000_000)
+    ap.add_argument("--queries", type=int, default=4000)
+    ap.add_argument("--top-l", type=int, default=64)
+    ap.add_argument("--search-width", type=int, default=2)
+    ap.add_argument("--top-n", type=int, default=32)
+    ap.add_argument("--entries", type=int, default=128)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--staged-table", action="store_true", help="build the query tables with tann_lut_build first")
+    a = ap.parse_args()
+    cfg = dataclasses.replace(synth.CONFIGS[a.config], num_nodes=a.nodes, components=max(1, a.nodes // 1000),
+                              num_queries=a.queries, kmeans_iters=5)
+    s = synth.build(cfg, "cuda")
+    ix = search.device_index_from_synth(s)
+    q = s.queries.cuda().contiguous()
+    if cfg.rvq:
+        model = search.rvq_model_from_synth(s)
+        (offs, ids, _), ms = _time(lambda: model.device_entry_batch(q, a.entries), a.reps)
+        print(f"rvq_entries {ms:.3f} ms")
+    else:
+        offs = torch.arange(a.queries + 1, dtype=torch.int32, device="cuda")
+        ids = torch.full((a.queries,), int(s.medoid), dtype=torch.int32, device="cuda")
+    p = search.TopologySearchParams(top_l=a.top_l, search_width=a.search_width, max_expansions=4096)
+    cap = p.capacity(a.top_n)
+    lut = None
+    if a.staged_table:
+        lut, ms = _time(lambda: search.lut_build(ix, q), a.reps)
+        print(f"lut_build {ms:.3f} ms")
+    (cand, stats), ms = _time(lambda: search.beam_search(ix, p, offs, ids, queries=None if lut is not None else q,
+                                                         lut=lut, capacity=cap), a.reps)
+    st = stats.cpu().numpy()
+    e, v = float(st[:, 1].mean()), float(st[:, 0].mean())
+    gbytes = a.queries * (e * 4 * ix.degree + v * ix.num_chunks) / 1e9
+    print(f"beam_search {ms:.3f} ms  nodes={a.nodes} queries={a.queries} L={a.top_l} C={cap} expanded/query={e:.1f} "
+          f"visited/query={v:.1f} algorithmic={gbytes:.3f} GB -> {gbytes / ms * 1e3:.1f} GB/s")
+    rp = search.RerankExactParams(top_k=10, top_n=a.top_n)
+    _, ms = _time(lambda: search.rerank_exact(ix, rp, cand, q), a.reps)
+    print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}")
+
+
+if __name__ == "__main__":
+    main()
