@@ -293,6 +293,22 @@ __device__ __noinline__ void BuildLutGeneric(float* lut, const float* sq, const 
     }
 }
 
+// Bitonic sort of one key per lane across a warp, ascending by lane.
+__device__ __forceinline__ unsigned long long WarpSortKey(unsigned long long k, uint32_t lane) {
+#pragma unroll
+    for (uint32_t size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(kFull, k, stride);
+            const bool upper = (lane & stride) != 0;          // this lane holds the pair's upper slot
+            const bool asc = (lane & size) == 0 || size == 32;
+            const bool take_min = upper != asc;
+            k = take_min ? (o < k ? o : k) : (o > k ? o : k);
+        }
+    }
+    return k;
+}
+
 // Bitonic sort of F keys held in shared memory (any power of two F).
 __device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
     for (uint32_t k = 2; k <= F; k <<= 1) {
@@ -338,7 +354,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
     float* sq = reinterpret_cast<float*>(offs + M + 1);
 
     __shared__ BeamCtl ctl;
-    __shared__ uint32_t s_surv;
+    __shared__ uint32_t s_surv, s_pass;
     __shared__ uint32_t s_sel[kBeamThreads / 32][TANN_MAX_SEARCH_WIDTH];  // selected nodes, one copy per warp
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31;
@@ -390,7 +406,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             ctl.ls_stage = 0; ctl.ls_has_prev = 0; ctl.ls_topk_changed = 0;
             ctl.ls_prev_dk = __int_as_float(0x7f800000);
             ctl.ls_prev_boundary = __int_as_float(0x7f800000);
-            s_surv = 0;
+            s_surv = 0; s_pass = 0;
         }
         if (tid < 32) ctl.ls_prev_ids[tid] = kInvalid;
         __syncthreads();
@@ -509,6 +525,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             // ---- phase 1: gather slot ids, Bloom tests ----------------------------------------
             unsigned long long my_key = kInvalidKey;  // kSingle: this thread's slot
             uint32_t my_words[kM > 0 ? kM / 4 : 1];     // kSingle: its code row
+            BloomBits my_bits;                          // kSingle: its visited-set positions
             if (!kSingle)
                 for (uint32_t i = tid; i < F; i += kBeamThreads) fkey[i] = kInvalidKey;
             const uint32_t rounds = kSingle ? 1u : (nslots + kBeamThreads - 1) / kBeamThreads;
@@ -534,7 +551,9 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         id = __ldg(row + j);
                     }
                 }
-                const bool pass = id != kInvalid && id < N && !BloomTest(id, bloom);
+                const BloomBits bits = BloomPositions(id);
+                const bool pass = id != kInvalid && id < N && !BloomTest(bits, bloom);
+                if (kSingle) my_bits = bits;
                 // The code row does not depend on the barrier below: request it now.
                 if constexpr (kSingle && kM > 0)
                     if (pass) LoadCodeWords<kM>(ShardRow(a.ix.codes, id, M), my_words);
@@ -548,7 +567,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     // (src/search/topology_search_kernel.cu:2543-2564). Same here, made explicit.
                     if (s < F) fkey[s] = parked;
                     __syncthreads();
-                    if (pass) BloomAdd(id, bloom);
+                    if (pass) BloomAdd(bits, bloom);
                     __syncthreads();
                 }
             }
@@ -565,7 +584,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 const bool pass = parked != kInvalidKey;
                 if (pass) {
                     const uint32_t id = (uint32_t)parked;
-                    if (kSingle) BloomAdd(id, bloom);
+                    if (kSingle) BloomAdd(my_bits, bloom);
                     float dist;
                     if constexpr (kSingle && kM > 0) {
                         dist = AdcFromWords<kM>(lut, my_words);
@@ -575,53 +594,94 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     const unsigned long long key = ((unsigned long long)OrderedBits(dist) << 32) | id;
                     if (kSingle) my_key = key; else fkey[s] = key;
                 }
-                fv += __syncthreads_count(pass);
+                if (!kSingle) fv += __syncthreads_count(pass);
             }
-            const uint32_t nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
             TANN_PHASE(3);  // 3: Bloom adds + code rows + table sums
 
-            // ---- order the frontier -----------------------------------------------------------
-            // sorted[0 .. n) = the frontier entries that can still enter the list, ascending.
+            // ---- order the frontier and merge it into the list (:1338-1424) ---------------------
+            // sorted[0 .. n) = the frontier entries that can still enter the list, ascending;
+            // entry x is accepted while sorted[x] < list[nv-1-x] (a prefix, the test is monotone).
             const unsigned long long* sorted;
-            uint32_t n;
+            uint32_t nv, accepted = 0;
             if (kSingle) {
-                // When the list is full an entry not below its last element can never be accepted
-                // (the acceptance test below compares entry a with element nv-1-a), so only the
-                // others are kept; they are compacted and rank-sorted (each survivor counts the
-                // survivors in front of it), which costs ~4 instructions per pair instead of a
-                // 28-step bitonic network over all 128 slots.
+                // When the list is full an entry not below its last element can never be accepted,
+                // so only the others are kept; they are compacted and rank-sorted (each survivor
+                // counts the survivors in front of it), which costs ~4 instructions per pair
+                // instead of a 28-step bitonic network over all 128 slots. The same thread then
+                // tests its entry for acceptance and finds its place in the list: an accepted entry
+                // is below list[nv - accepted], so its lower bound in the whole list is also its
+                // lower bound among the elements that stay.
+                const bool pass = my_key != kInvalidKey;
                 const unsigned long long thr = valid == C ? (cur[C - 1] & kCmpMask) : ~0ull;
-                const bool surv = my_key != kInvalidKey && my_key < thr;
+                const bool surv = pass && my_key < thr;
+                const uint32_t ballot_pass = __ballot_sync(kFull, pass);
                 const uint32_t ballot = __ballot_sync(kFull, surv);
                 uint32_t base = 0;
-                if (lane == 0 && ballot != 0u) base = atomicAdd(&s_surv, (uint32_t)__popc(ballot));
+                if (lane == 0) {
+                    if (ballot != 0u) base = atomicAdd(&s_surv, (uint32_t)__popc(ballot));
+                    if (ballot_pass != 0u) atomicAdd(&s_pass, (uint32_t)__popc(ballot_pass));
+                }
                 base = __shfl_sync(kFull, base, 0);
                 if (surv) fkey[base + __popc(ballot & ((1u << lane) - 1u))] = my_key;
                 __syncthreads();
-                n = s_surv;
-                if (tid < n) {
-                    const unsigned long long k = fkey[tid];
-                    uint32_t rank = 0;
+                const uint32_t n = s_surv;
+                fv = s_pass;
+                nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
+                bool pred = false;
+                unsigned long long k = kInvalidKey;
+                uint32_t rank = 0;
+                if (n > 32) {
+                    // Long survivor lists (the list is not full yet): every warp sorts its 32 keys
+                    // with shuffles, then a key's rank is its place in its own run plus its lower /
+                    // upper bounds in the other runs (runs in front win ties, so ranks are distinct).
+                    k = tid < n ? fkey[tid] : kInvalidKey;
+                    k = WarpSortKey(k, lane);
+                    fkey[tid] = k;
+                    __syncthreads();
+                    rank = lane;
+                    const uint32_t w = tid >> 5;
+#pragma unroll
+                    for (uint32_t o = 0; o < kBeamThreads / 32; ++o) {
+                        if (o == w) continue;
+                        const unsigned long long* run = fkey + o * 32;
+                        uint32_t lo = 0, hi = 32;
+                        while (lo < hi) {
+                            const uint32_t mid = (lo + hi) >> 1;
+                            const unsigned long long x = run[mid];
+                            if (o < w ? x <= k : x < k) lo = mid + 1; else hi = mid;
+                        }
+                        rank += lo;
+                    }
+                } else if (tid < n) {
+                    k = fkey[tid];
                     for (uint32_t j = 0; j < n; ++j) {
                         const unsigned long long kj = fkey[j];
                         rank += (kj < k || (kj == k && j < tid)) ? 1u : 0u;
                     }
-                    skey[rank] = k;
                 }
-                __syncthreads();
-                if (tid == 0) s_surv = 0;
+                if (k != kInvalidKey) {
+                    skey[rank] = k;
+                    if (rank < nv) pred = k < (cur[nv - 1 - rank] & kCmpMask);
+                    if (pred) {
+                        uint32_t lo = 0, hi = valid;  // list elements < k stay in front of it
+                        while (lo < hi) {
+                            const uint32_t mid = (lo + hi) >> 1;
+                            if ((cur[mid] & kCmpMask) < k) lo = mid + 1; else hi = mid;
+                        }
+                        nxt[rank + lo] = k;
+                        if (rank + lo < a.p.learned_stop.top_k) ctl.ls_topk_changed = 1;
+                    }
+                }
+                accepted = __syncthreads_count(pred);
+                if (tid == 0) { s_surv = 0; s_pass = 0; }
                 sorted = skey;
+                TANN_PHASE(4);  // 4: filter + compaction + rank sort + acceptance
             } else {
+                nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
                 SortKeysShared(fkey, F);
                 sorted = fkey;
-                n = fv;
-            }
-
-            TANN_PHASE(4);  // 4: filter + compaction + rank sort
-            // ---- merge (:1338-1424) as a parallel merge-path --------------------------------------
-            uint32_t accepted = 0;
-            {
-                const uint32_t lim = min(n, nv);
+                TANN_PHASE(4);
+                const uint32_t lim = min(fv, nv);
                 uint32_t base = 0;
                 do {
                     const uint32_t x = base + tid;
@@ -629,9 +689,22 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     if (x < lim) pred = sorted[x] < (cur[nv - 1 - x] & kCmpMask);
                     const uint32_t cnt = __syncthreads_count(pred);
                     accepted += cnt;
-                    if (cnt < (uint32_t)kBeamThreads) break;  // the predicate is monotone in x
+                    if (cnt < (uint32_t)kBeamThreads) break;
                     base += kBeamThreads;
                 } while (base < lim);
+                const uint32_t kept = nv - accepted;
+                bool changed = false;
+                for (uint32_t j = tid; j < accepted; j += kBeamThreads) {
+                    const unsigned long long fk = sorted[j];
+                    uint32_t lo = 0, hi = kept;  // kept candidates < fk stay in front of it
+                    while (lo < hi) {
+                        const uint32_t mid = (lo + hi) >> 1;
+                        if ((cur[mid] & kCmpMask) < fk) lo = mid + 1; else hi = mid;
+                    }
+                    nxt[j + lo] = fk;
+                    changed |= (j + lo) < a.p.learned_stop.top_k;
+                }
+                if (changed) ctl.ls_topk_changed = 1;
             }
             if (accepted != 0) {
                 const uint32_t kept = nv - accepted;
@@ -645,19 +718,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     }
                     nxt[i + lo] = c;
                 }
-                bool changed = false;
-                for (uint32_t j = tid; j < accepted; j += kBeamThreads) {
-                    const unsigned long long fk = sorted[j];
-                    uint32_t lo = 0, hi = kept;  // kept candidates < fk stay in front of it
-                    while (lo < hi) {
-                        const uint32_t mid = (lo + hi) >> 1;
-                        if ((cur[mid] & kCmpMask) < fk) lo = mid + 1; else hi = mid;
-                    }
-                    nxt[j + lo] = fk;
-                    changed |= (j + lo) < a.p.learned_stop.top_k;
-                }
                 for (uint32_t i = nv + tid; i < C; i += kBeamThreads) nxt[i] = kInvalidKey;
-                if (changed) ctl.ls_topk_changed = 1;
                 unsigned long long* t = cur; cur = nxt; nxt = t;
             }
             valid = nv;

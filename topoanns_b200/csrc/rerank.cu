@@ -9,6 +9,12 @@
 // (distance, id) (:92-100,153-204). uint8 queries on uint8 vectors with dim <= 256 take an integer
 // path (|a-b| per byte, dp4a square-accumulate): every partial sum of the reference's float
 // accumulation is then an integer below 2^24, so both give the same bits.
+//
+// Work split: one thread per rank reads the candidate record, applies the bound filter and works
+// out the vector's address; then 8 lanes per candidate ("octet") read the row with 16-byte loads,
+// several candidates per octet in flight. For float rows octet lane p owns the reference's lanes
+// 4p..4p+3 (dims 32k+4p..32k+4p+3, ascending k), so every partial sum and every tree step is the
+// reference's. Rows that do not start on 16-byte boundaries take a warp-per-candidate path.
 #include "tann_common.cuh"
 #include "tann_launch.h"
 
@@ -18,21 +24,173 @@ constexpr int kRerankThreads = 128;
 constexpr unsigned long long kInvalidKey64 = 0xff800000ffffffffull;
 
 __device__ __forceinline__ const uint8_t* VectorPtr(const TannIndexView& ix, uint32_t id) {
-    uint64_t local = id;
+    uint32_t local = id;
     const uint8_t* base = static_cast<const uint8_t*>(ix.vectors.base[0]);
     if (ix.vectors.num_shards > 1) {
         const uint64_t shard = id / ix.vectors.rows_per_shard;
-        local = id - shard * ix.vectors.rows_per_shard;
+        local = (uint32_t)(id - shard * ix.vectors.rows_per_shard);
         base = static_cast<const uint8_t*>(ix.vectors.base[shard]);
     }
     // src/io/vector_page_layout.cpp:50-57
-    return base + (local / ix.vectors_per_page) * ix.page_bytes + (local % ix.vectors_per_page) * ix.vector_bytes;
+    const uint32_t page = local / ix.vectors_per_page;
+    const uint32_t slot = local - page * ix.vectors_per_page;
+    return base + (uint64_t)page * ix.page_bytes + (uint64_t)slot * ix.vector_bytes;
 }
 
 __device__ __forceinline__ float LowerBoundSq(float approx_sq, float err) {
     const float a = sqrtf(fmaxf(approx_sq, 0.0f));
     const float lo = fmaxf(0.0f, a - err);
     return lo * lo;
+}
+
+__device__ __forceinline__ uint32_t SqDiffBytes(uint32_t a, uint32_t b, uint32_t acc) {
+    const uint32_t ad = __vabsdiffu4(a, b);
+    return __dp4a(ad, ad, acc);
+}
+
+// Integer rows: kStep candidates per octet and step; dim / 16 sixteen-byte pieces per row.
+template <uint32_t kStep>
+__device__ __forceinline__ void OctetRanksInt(unsigned long long* keys, const uint32_t* rank_ids,
+                                              const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
+                                              uint32_t octet, uint32_t ol) {
+    const uint32_t pieces = dim / 16;
+    // The loop bound is the warp's first octet, so all 32 lanes make the same number of trips (the
+    // shuffles below need every lane); octets past the end carry invalid slots and write nothing.
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+        const uint32_t r0 = w0 + (octet & 3u) * kStep;
+        unsigned long long ptr[kStep];
+        uint32_t acc[kStep];
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+            ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
+            acc[g] = 0;
+        }
+        for (uint32_t j = ol; j < pieces; j += 8) {
+            uint4 v[kStep];
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                v[g] = ptr[g] != kInvalidKey64 ? __ldg(reinterpret_cast<const uint4*>(ptr[g]) + j)
+                                               : make_uint4(0, 0, 0, 0);
+            const uint4 qv = reinterpret_cast<const uint4*>(qrow)[j];
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g) {
+                acc[g] = SqDiffBytes(v[g].x, qv.x, acc[g]);
+                acc[g] = SqDiffBytes(v[g].y, qv.y, acc[g]);
+                acc[g] = SqDiffBytes(v[g].z, qv.z, acc[g]);
+                acc[g] = SqDiffBytes(v[g].w, qv.w, acc[g]);
+            }
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+            acc[g] += __shfl_xor_sync(kFull, acc[g], 4);
+            acc[g] += __shfl_xor_sync(kFull, acc[g], 2);
+            acc[g] += __shfl_xor_sync(kFull, acc[g], 1);
+        }
+        if (ol == 0) {
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                if (ptr[g] != kInvalidKey64) keys[r0 + g] = KeyOf(static_cast<float>(acc[g]), rank_ids[r0 + g]);
+        }
+    }
+}
+
+// Float rows with float queries, dim a multiple of 4.
+template <uint32_t kStep>
+__device__ __forceinline__ void OctetRanksF32(unsigned long long* keys, const uint32_t* rank_ids,
+                                              const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
+                                              uint32_t octet, uint32_t ol) {
+    // The loop bound is the warp's first octet, so all 32 lanes make the same number of trips (the
+    // shuffles below need every lane); octets past the end carry invalid slots and write nothing.
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+        const uint32_t r0 = w0 + (octet & 3u) * kStep;
+        unsigned long long ptr[kStep];
+        float acc[kStep][4];
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+            ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
+            acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+        }
+        for (uint32_t d0 = 4 * ol; d0 < dim; d0 += 32) {
+            float4 v[kStep];
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                v[g] = ptr[g] != kInvalidKey64 ? __ldg(reinterpret_cast<const float4*>(ptr[g] + 4ull * d0))
+                                               : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            const float4 qv = *reinterpret_cast<const float4*>(qrow + 4u * d0);
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g) {
+                float df = v[g].x - qv.x; acc[g][0] = fmaf(df, df, acc[g][0]);
+                df = v[g].y - qv.y; acc[g][1] = fmaf(df, df, acc[g][1]);
+                df = v[g].z - qv.z; acc[g][2] = fmaf(df, df, acc[g][2]);
+                df = v[g].w - qv.w; acc[g][3] = fmaf(df, df, acc[g][3]);
+            }
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+            // tree steps 16, 8, 4 of the reference's 32 lanes = octet lanes +4, +2, +1
+#pragma unroll
+            for (int off = 4; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[g][i] += __shfl_down_sync(kFull, acc[g][i], off, 8);
+            }
+            acc[g][0] += acc[g][2];   // step 2
+            acc[g][1] += acc[g][3];
+            acc[g][0] += acc[g][1];   // step 1
+        }
+        if (ol == 0) {
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                if (ptr[g] != kInvalidKey64) keys[r0 + g] = KeyOf(acc[g][0], rank_ids[r0 + g]);
+        }
+    }
+}
+
+// uint8 rows with float queries that are not uint8-valued: the same lane ownership as the float
+// rows, four bytes per lane and 32 dims.
+template <uint32_t kStep>
+__device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const uint32_t* rank_ids,
+                                                const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
+                                                uint32_t octet, uint32_t ol) {
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+        const uint32_t r0 = w0 + (octet & 3u) * kStep;
+        unsigned long long ptr[kStep];
+        float acc[kStep][4];
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+            ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
+            acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+        }
+        for (uint32_t d0 = 4 * ol; d0 < dim; d0 += 32) {
+            uint32_t v[kStep];
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                v[g] = ptr[g] != kInvalidKey64 ? __ldg(reinterpret_cast<const uint32_t*>(ptr[g] + d0)) : 0u;
+            const float4 qv = *reinterpret_cast<const float4*>(qrow + 4u * d0);
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g) {
+                float df = static_cast<float>(v[g] & 0xffu) - qv.x; acc[g][0] = fmaf(df, df, acc[g][0]);
+                df = static_cast<float>((v[g] >> 8) & 0xffu) - qv.y; acc[g][1] = fmaf(df, df, acc[g][1]);
+                df = static_cast<float>((v[g] >> 16) & 0xffu) - qv.z; acc[g][2] = fmaf(df, df, acc[g][2]);
+                df = static_cast<float>(v[g] >> 24) - qv.w; acc[g][3] = fmaf(df, df, acc[g][3]);
+            }
+        }
+#pragma unroll
+        for (uint32_t g = 0; g < kStep; ++g) {
+#pragma unroll
+            for (int off = 4; off >= 1; off >>= 1) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[g][i] += __shfl_down_sync(kFull, acc[g][i], off, 8);
+            }
+            acc[g][0] += acc[g][2];
+            acc[g][1] += acc[g][3];
+            acc[g][0] += acc[g][1];
+        }
+        if (ol == 0) {
+#pragma unroll
+            for (uint32_t g = 0; g < kStep; ++g)
+                if (ptr[g] != kInvalidKey64) keys[r0 + g] = KeyOf(acc[g][0], rank_ids[r0 + g]);
+        }
+    }
 }
 
 __global__ void __launch_bounds__(kRerankThreads)
@@ -42,8 +200,11 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
               uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts,
               const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag) {
     extern __shared__ __align__(16) unsigned char rr_smem[];
+    // keys[r] first holds the address of candidate r's vector (or the invalid key when the rank is
+    // empty or filtered), then its (distance, id) sort key.
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(rr_smem);   // [padded]
-    uint8_t* qrow = reinterpret_cast<uint8_t*>(keys + padded);                   // query row copy
+    uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
+    uint8_t* qrow = rr_smem + (((size_t)padded * 12 + 15) & ~(size_t)15);          // query row copy, 16-byte aligned
     __shared__ float s_threshold, s_qnorm;
     __shared__ unsigned int s_exact, s_filtered;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -57,11 +218,23 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
     if (swap_queries) { queries = queries_u8; qkind = TANN_KIND_UINT8; }
     const uint32_t qbytes = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
     const uint32_t tile = p.tile == 0 ? p.top_n : p.tile;
+    // Rows that start on 16-byte boundaries are read with 16-byte loads by 8 lanes per candidate.
+    const bool rows16 = (ix.vector_bytes % 16 == 0) && (ix.page_bytes % 16 == 0);
+    const bool octet_int = int_path && rows16 && (dim % 16 == 0);
+    const bool octet_f32 = !int_path && rows16 && ix.vector_kind == TANN_KIND_FLOAT32 &&
+                           qkind == TANN_KIND_FLOAT32 && (dim % 4 == 0);
+    const bool octet_u8f32 = !int_path && ix.vector_kind == TANN_KIND_UINT8 && qkind == TANN_KIND_FLOAT32 &&
+                             (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0) && (dim % 4 == 0);
     unsigned long long tot_exact = 0, tot_filtered = 0;
 
     for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
         const uint8_t* qsrc = static_cast<const uint8_t*>(queries) + q * qbytes;
-        for (uint32_t i = tid; i < qbytes; i += kRerankThreads) qrow[i] = qsrc[i];
+        if (qbytes % 16 == 0) {
+            for (uint32_t i = tid; i < qbytes / 16; i += kRerankThreads)
+                reinterpret_cast<uint4*>(qrow)[i] = __ldg(reinterpret_cast<const uint4*>(qsrc) + i);
+        } else {
+            for (uint32_t i = tid; i < qbytes; i += kRerankThreads) qrow[i] = qsrc[i];
+        }
         for (uint32_t i = tid; i < padded; i += kRerankThreads) keys[i] = kInvalidKey64;
         if (tid == 0) {
             s_threshold = __int_as_float(0x7f800000);
@@ -76,90 +249,104 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
             }
             s_qnorm = (float)s;
         }
-        __syncthreads();
+        if (p.use_bound_filter) __syncthreads();
         for (uint32_t rb = 0; rb < p.top_n; rb += tile) {
             const uint32_t rc = min(tile, p.top_n - rb);
             const float threshold = s_threshold;
-            // A warp scores kGroup candidates per step: all their row loads are issued before any
-            // reduction, so several random 128-byte (or longer) reads are in flight per lane.
-            constexpr uint32_t kGroup = 4;
-            for (uint32_t r0 = rb + warp * kGroup; r0 < rb + rc; r0 += (kRerankThreads / 32) * kGroup) {
-                const uint8_t* vptr[kGroup];
-                uint32_t ids[kGroup];
-                bool act[kGroup];
-#pragma unroll
-                for (uint32_t g = 0; g < kGroup; ++g) {
-                    const uint32_t r = r0 + g;
-                    act[g] = false;
-                    ids[g] = kInvalid;
-                    vptr[g] = nullptr;
-                    if (r >= rb + rc || r >= capacity) continue;
+            // ---- one thread per rank: candidate record, bound filter, vector address ----------
+            uint32_t n_act = 0, n_flt = 0;
+            for (uint32_t r = rb + tid; r < rb + rc; r += kRerankThreads) {
+                unsigned long long slot = kInvalidKey64;
+                if (r < capacity) {
                     const Cand c = cand[q * capacity + r];
-                    if (c.id == kInvalid) continue;
                     const uint32_t id = c.id & kRawMask;
-                    if (id >= ix.num_nodes) continue;
-                    if (p.use_bound_filter && isfinite(threshold)) {
-                        if (LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id)) > threshold) {
-                            if (lane == 0) atomicAdd(&s_filtered, 1u);
-                            continue;
+                    if (c.id != kInvalid && id < ix.num_nodes) {
+                        bool keep = true;
+                        if (p.use_bound_filter && isfinite(threshold))
+                            keep = !(LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id)) > threshold);
+                        if (keep) {
+                            slot = reinterpret_cast<unsigned long long>(VectorPtr(ix, id));
+                            rank_ids[r] = id;
+                            ++n_act;
+                        } else {
+                            ++n_flt;
                         }
                     }
-                    act[g] = true;
-                    ids[g] = id;
-                    vptr[g] = VectorPtr(ix, id);
                 }
-                float dist[kGroup];
-                if (int_path) {
-                    uint32_t acc[kGroup];
-#pragma unroll
-                    for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0;
-                    const uint32_t* q4 = reinterpret_cast<const uint32_t*>(qrow);
-                    for (uint32_t i = lane; i < dim / 4; i += 32) {
-                        uint32_t w[kGroup];
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g)
-                            w[g] = act[g] ? __ldg(reinterpret_cast<const uint32_t*>(vptr[g]) + i) : 0u;
-                        const uint32_t qw = q4[i];
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g) {
-                            const uint32_t ad = __vabsdiffu4(w[g], qw);
-                            acc[g] = __dp4a(ad, ad, acc[g]);
-                        }
-                    }
+                keys[r] = slot;
+            }
+            if (n_act) atomicAdd(&s_exact, n_act);
+            if (n_flt) atomicAdd(&s_filtered, n_flt);
+            __syncthreads();
+            // ---- distances --------------------------------------------------------------------
+            const uint32_t end = rb + rc;
+            if (octet_int) {
+                if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+            } else if (octet_f32) {
+                if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                else OctetRanksF32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+            } else if (octet_u8f32) {
+                if (rc >= 64) OctetRanksU8F32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                else OctetRanksU8F32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+            } else {
+                // A warp scores kGroup candidates per step: all their row loads are issued before any
+                // reduction, so several random reads are in flight per lane.
+                constexpr uint32_t kGroup = 4;
+                for (uint32_t r0 = rb + warp * kGroup; r0 < end; r0 += (kRerankThreads / 32) * kGroup) {
+                    const uint8_t* vptr[kGroup];
+                    bool act[kGroup];
 #pragma unroll
                     for (uint32_t g = 0; g < kGroup; ++g) {
-#pragma unroll
-                        for (int off = 16; off >= 1; off >>= 1) acc[g] += __shfl_xor_sync(kFull, acc[g], off);
-                        dist[g] = static_cast<float>(acc[g]);
+                        const unsigned long long slot = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
+                        act[g] = slot != kInvalidKey64;
+                        vptr[g] = reinterpret_cast<const uint8_t*>(slot);
                     }
-                } else {
-                    float acc[kGroup];
+                    float dist[kGroup];
+                    if (int_path) {
+                        uint32_t acc[kGroup];
 #pragma unroll
-                    for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0.0f;
-                    for (uint32_t i = lane; i < dim; i += 32) {
-                        float v[kGroup];
+                        for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0;
+                        const uint32_t* q4 = reinterpret_cast<const uint32_t*>(qrow);
+                        for (uint32_t i = lane; i < dim / 4; i += 32) {
+                            uint32_t w[kGroup];
 #pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g)
-                            v[g] = act[g] ? LoadAsFloat<float>(vptr[g], ix.vector_kind, i) : 0.0f;
-                        const float qv = LoadAsFloat<float>(qrow, qkind, i);
+                            for (uint32_t g = 0; g < kGroup; ++g)
+                                w[g] = act[g] ? __ldg(reinterpret_cast<const uint32_t*>(vptr[g]) + i) : 0u;
+                            const uint32_t qw = q4[i];
+#pragma unroll
+                            for (uint32_t g = 0; g < kGroup; ++g) acc[g] = SqDiffBytes(w[g], qw, acc[g]);
+                        }
 #pragma unroll
                         for (uint32_t g = 0; g < kGroup; ++g) {
-                            const float diff = v[g] - qv;
-                            acc[g] = fmaf(diff, diff, acc[g]);
+#pragma unroll
+                            for (int off = 16; off >= 1; off >>= 1) acc[g] += __shfl_xor_sync(kFull, acc[g], off);
+                            dist[g] = static_cast<float>(acc[g]);
                         }
-                    }
+                    } else {
+                        float acc[kGroup];
 #pragma unroll
-                    for (uint32_t g = 0; g < kGroup; ++g) dist[g] = WarpTreeSum(acc[g]);
-                }
-                if (lane == 0) {
-                    uint32_t n = 0;
+                        for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0.0f;
+                        for (uint32_t i = lane; i < dim; i += 32) {
+                            float v[kGroup];
 #pragma unroll
-                    for (uint32_t g = 0; g < kGroup; ++g) {
-                        if (!act[g]) continue;
-                        keys[r0 + g] = KeyOf(dist[g], ids[g]);
-                        ++n;
+                            for (uint32_t g = 0; g < kGroup; ++g)
+                                v[g] = act[g] ? LoadAsFloat<float>(vptr[g], ix.vector_kind, i) : 0.0f;
+                            const float qv = LoadAsFloat<float>(qrow, qkind, i);
+#pragma unroll
+                            for (uint32_t g = 0; g < kGroup; ++g) {
+                                const float diff = v[g] - qv;
+                                acc[g] = fmaf(diff, diff, acc[g]);
+                            }
+                        }
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g) dist[g] = WarpTreeSum(acc[g]);
                     }
-                    if (n) atomicAdd(&s_exact, n);
+                    if (lane == 0) {
+#pragma unroll
+                        for (uint32_t g = 0; g < kGroup; ++g)
+                            if (act[g]) keys[r0 + g] = KeyOf(dist[g], rank_ids[r0 + g]);
+                    }
                 }
             }
             __syncthreads();
@@ -231,7 +418,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     uint32_t padded = 1;
     while (padded < p.top_n) padded <<= 1;
     const size_t qbytes = (size_t)ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
-    const size_t smem = (size_t)padded * 8 + ((qbytes + 15) & ~(size_t)15);
+    const size_t smem = (((size_t)padded * 12 + 15) & ~(size_t)15) + ((qbytes + 15) & ~(size_t)15);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rerank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              (int)smem);

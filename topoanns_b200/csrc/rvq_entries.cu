@@ -13,7 +13,7 @@
 namespace tann {
 
 constexpr int kRvqThreads = 256;
-constexpr int kRvqQueriesPerBlock = 4;
+constexpr int kRvqQueriesPerBlock = 8;
 
 // |x|^2 in the order of the reference's L2NormKernel (distance_kernel.cu:25-111): 128 "threads"
 // take columns t, t+128, ... with FMA, each warp runs the shuffle tree, and the four warp sums
@@ -48,23 +48,26 @@ __device__ __forceinline__ ArgMin Better(ArgMin a, ArgMin b) {
     if (b.d < a.d || (b.d == a.d && b.idx < a.idx)) return b;
     return a;
 }
-__device__ __forceinline__ ArgMin BlockArgMin(ArgMin v, ArgMin* scratch /*[8]*/) {
+
+// The same sum as NormBy128 by ONE warp: lane l plays threads l, 32 + l, 64 + l, 96 + l of the
+// 128 in turn (x is read with stride `stride`). All lanes return the result.
+__device__ __forceinline__ float NormByWarp(const float* x, uint32_t stride, uint32_t dim, uint32_t lane) {
+    float s[4];
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        ArgMin o;
-        o.d = __shfl_xor_sync(kFull, v.d, off);
-        o.idx = __shfl_xor_sync(kFull, v.idx, off);
-        v = Better(v, o);
+    for (uint32_t v = 0; v < 4; ++v) {
+        float acc = 0.0f;
+        for (uint32_t col = v * 32 + lane; col < dim; col += 128) {
+            const float xv = x[(size_t)col * stride];
+            acc = fmaf(xv, xv, acc);
+        }
+        s[v] = __shfl_sync(kFull, WarpTreeSum(acc), 0);
     }
-    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-    __syncthreads();
-    ArgMin r = scratch[0];
-#pragma unroll
-    for (int w = 1; w < kRvqThreads / 32; ++w) r = Better(r, scratch[w]);
-    __syncthreads();
-    return r;
+    return (s[0] + s[2]) + (s[1] + s[3]);
 }
 
+// One block scores kRvqQueriesPerBlock queries against a 256-entry codebook level: thread c owns
+// centroid c (codebooks are stored transposed, so a warp reads 128 contiguous bytes per dim), the
+// queries sit transposed in shared memory so that one 16-byte broadcast load feeds four FMAs.
 __global__ void __launch_bounds__(kRvqThreads)
 rvq_entries_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t dim,
                    const float* __restrict__ coarse, const float* __restrict__ coarse_t,
@@ -74,31 +77,33 @@ rvq_entries_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t dim,
                    const uint32_t* __restrict__ cluster_ids, uint32_t entry_count, uint32_t fallback,
                    int32_t* __restrict__ out_clusters, uint32_t* __restrict__ out_entry_ids,
                    uint32_t* __restrict__ out_entry_offsets) {
-    extern __shared__ float rvq_smem[];
-    float* x = rvq_smem;  // [kRvqQueriesPerBlock][dim], queries then residuals
-    __shared__ float ws[4];
-    __shared__ float norms[kRvqQueriesPerBlock];
-    __shared__ ArgMin scratch[kRvqThreads / 32];
-    __shared__ int best_coarse[kRvqQueriesPerBlock];
-    __shared__ int best_cluster[kRvqQueriesPerBlock];
     constexpr int QB = kRvqQueriesPerBlock;
-    const uint32_t tid = threadIdx.x;
+    constexpr int kWarps = kRvqThreads / 32;
+    extern __shared__ __align__(16) float rvq_smem[];
+    float* x = rvq_smem;  // [dim][QB]: queries, then residuals
+    __shared__ float norms[QB];
+    __shared__ ArgMin scratch[kWarps][QB];
+    __shared__ int best_coarse[QB];
+    __shared__ int best_cluster[QB];
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     if (blockIdx.x == 0 && out_entry_offsets != nullptr)
         for (uint64_t i = tid; i <= Q; i += kRvqThreads) out_entry_offsets[i] = (uint32_t)(i * entry_count);
 
     for (uint64_t q0 = (uint64_t)blockIdx.x * QB; q0 < Q; q0 += (uint64_t)gridDim.x * QB) {
         const int nq = (int)min((uint64_t)QB, Q - q0);
-        for (uint32_t i = tid; i < (uint32_t)nq * dim; i += kRvqThreads) x[i] = queries[q0 * dim + i];
+        for (uint32_t i = tid; i < (uint32_t)QB * dim; i += kRvqThreads) {
+            const uint32_t qi = i / dim, k = i - qi * dim;
+            x[k * QB + qi] = (int)qi < nq ? queries[q0 * dim + i] : 0.0f;
+        }
         __syncthreads();
         for (int level = 0; level < 2; ++level) {
-            // norms of the (residual) queries
-            for (int qi = 0; qi < nq; ++qi) {
-                if (tid < 128) NormBy128(x + (size_t)qi * dim, dim, ws);
-                __syncthreads();
-                if (tid == 0) norms[qi] = (ws[0] + ws[2]) + (ws[1] + ws[3]);
-                __syncthreads();
+            // norms of the (residual) queries, one warp per query
+            for (int qi = warp; qi < nq; qi += kWarps) {
+                const float n2 = NormByWarp(x + qi, QB, dim, lane);
+                if (lane == 0) norms[qi] = n2;
             }
+            __syncthreads();
             const float* book_t = level == 0 ? coarse_t : fine_t;
             const float* book_norms = level == 0 ? coarse_norms : fine_norms;
             const uint32_t count = level == 0 ? nc : nf;
@@ -109,10 +114,17 @@ rvq_entries_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t dim,
                 float dot[QB];
 #pragma unroll
                 for (int qi = 0; qi < QB; ++qi) dot[qi] = 0.0f;
+#pragma unroll 4
                 for (uint32_t k = 0; k < dim; ++k) {
                     const float w = __ldg(book_t + (size_t)k * count + c);
 #pragma unroll
-                    for (int qi = 0; qi < QB; ++qi) dot[qi] = fmaf(x[qi * dim + k], w, dot[qi]);
+                    for (int g = 0; g < QB / 4; ++g) {
+                        const float4 xv = *reinterpret_cast<const float4*>(x + k * QB + 4 * g);
+                        dot[4 * g + 0] = fmaf(xv.x, w, dot[4 * g + 0]);
+                        dot[4 * g + 1] = fmaf(xv.y, w, dot[4 * g + 1]);
+                        dot[4 * g + 2] = fmaf(xv.z, w, dot[4 * g + 2]);
+                        dot[4 * g + 3] = fmaf(xv.w, w, dot[4 * g + 3]);
+                    }
                 }
                 const float cn = book_norms[c];
 #pragma unroll
@@ -127,25 +139,37 @@ rvq_entries_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t dim,
                         // :66-81: starts from FLT_MAX and skips empty buckets
                         ok = D < FLT_MAX && bucket_sizes[(size_t)best_coarse[qi] * nf + c] > 0;
                     }
-                    if (ok) {
-                        best[qi] = Better(best[qi], ArgMin{D, (int)c});
-                    }
+                    if (ok) best[qi] = Better(best[qi], ArgMin{D, (int)c});
                 }
             }
-            for (int qi = 0; qi < nq; ++qi) {
-                const ArgMin r = BlockArgMin(best[qi], scratch);
-                if (tid == 0) {
-                    const int idx = r.idx == 0x7fffffff ? 0 : r.idx;
-                    if (level == 0) best_coarse[qi] = idx;
-                    else best_cluster[qi] = best_coarse[qi] * (int)nf + idx;
+            // block argmin of all queries at once: warp shuffles, then one thread per query
+#pragma unroll
+            for (int qi = 0; qi < QB; ++qi) {
+                ArgMin v = best[qi];
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    ArgMin o;
+                    o.d = __shfl_xor_sync(kFull, v.d, off);
+                    o.idx = __shfl_xor_sync(kFull, v.idx, off);
+                    v = Better(v, o);
                 }
+                if (lane == 0) scratch[warp][qi] = v;
+            }
+            __syncthreads();
+            if ((int)tid < nq) {
+                ArgMin r = scratch[0][tid];
+#pragma unroll
+                for (int w = 1; w < kWarps; ++w) r = Better(r, scratch[w][tid]);
+                const int idx = r.idx == 0x7fffffff ? 0 : r.idx;
+                if (level == 0) best_coarse[tid] = idx;
+                else best_cluster[tid] = best_coarse[tid] * (int)nf + idx;
             }
             __syncthreads();
             if (level == 0) {
                 // residual, RVQ.cu:180-188
                 for (uint32_t i = tid; i < (uint32_t)nq * dim; i += kRvqThreads) {
                     const uint32_t qi = i / dim, k = i - qi * dim;
-                    x[i] = x[i] - coarse[(size_t)best_coarse[qi] * dim + k];
+                    x[k * QB + qi] = x[k * QB + qi] - coarse[(size_t)best_coarse[qi] * dim + k];
                 }
                 __syncthreads();
             }

@@ -53,22 +53,28 @@ __device__ __forceinline__ uint32_t BloomHash(int h, uint32_t v) {
     v ^= v >> 16;
     return v & (kBloomWords * 32 - 1);
 }
-__device__ __forceinline__ bool BloomTest(uint32_t v, const uint32_t* words) {
+// The three bit positions of a value; computed once and used for the test and, later, the add.
+struct BloomBits {
+    uint32_t b[3];
+};
+__device__ __forceinline__ BloomBits BloomPositions(uint32_t v) {
+    BloomBits r;
+#pragma unroll
+    for (int h = 0; h < 3; ++h) r.b[h] = BloomHash(h, v);
+    return r;
+}
+__device__ __forceinline__ bool BloomTest(const BloomBits& p, const uint32_t* words) {
     bool ok = true;
 #pragma unroll
-    for (int h = 0; h < 3; ++h) {
-        const uint32_t bit = BloomHash(h, v);
-        ok &= ((words[bit & (kBloomWords - 1)] >> (bit >> 10)) & 1u) != 0u;
-    }
+    for (int h = 0; h < 3; ++h) ok &= ((words[p.b[h] & (kBloomWords - 1)] >> (p.b[h] >> 10)) & 1u) != 0u;
     return ok;
 }
-__device__ __forceinline__ void BloomAdd(uint32_t v, uint32_t* words) {
+__device__ __forceinline__ void BloomAdd(const BloomBits& p, uint32_t* words) {
 #pragma unroll
-    for (int h = 0; h < 3; ++h) {
-        const uint32_t bit = BloomHash(h, v);
-        atomicOr(&words[bit & (kBloomWords - 1)], 1u << (bit >> 10));
-    }
+    for (int h = 0; h < 3; ++h) atomicOr(&words[p.b[h] & (kBloomWords - 1)], 1u << (p.b[h] >> 10));
 }
+__device__ __forceinline__ bool BloomTest(uint32_t v, const uint32_t* words) { return BloomTest(BloomPositions(v), words); }
+__device__ __forceinline__ void BloomAdd(uint32_t v, uint32_t* words) { BloomAdd(BloomPositions(v), words); }
 
 // Resolve row `n` of a sharded array; rows are `row_bytes` apart inside a shard.
 __device__ __forceinline__ const uint8_t* ShardRow(const TannShards& s, uint64_t n, uint64_t row_bytes) {

@@ -65,7 +65,12 @@ def main() -> None:
           f"visited/query={v:.1f} algorithmic={gbytes:.3f} GB -> {gbytes / ms * 1e3:.1f} GB/s")
     rp = search.RerankExactParams(top_k=10, top_n=a.top_n)
     _, ms = _time(lambda: search.rerank_exact(ix, rp, cand, q), a.reps)
-    print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}")
+    print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}  (float32 queries)")
+    if s.vectors.dtype == torch.uint8:
+        q8 = q.to(torch.uint8).contiguous()   # the searcher makes this copy on the device when the values allow it
+        _, ms = _time(lambda: search.rerank_exact(ix, rp, cand, q8), a.reps)
+        gb = a.queries * a.top_n * s.vectors.shape[1] / 1e9
+        print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}  (uint8 queries, integer path) {gb / ms * 1e3:.1f} GB/s")
 
 
 if __name__ == "__main__":
