@@ -233,6 +233,24 @@ TannStatus tann_topk_pack(const float* dists /*dev [Q][top_n]*/, const uint32_t*
                           uint32_t top_n, uint32_t top_k, float* out_dists /*dev [Q][top_k]*/,
                           uint32_t* out_ids, tann_stream_t stream);
 
+/* Exact rerank + top-k of one batch (tann_rerank_exact followed by tann_topk_pack, same results)
+ * that allocates nothing: its work space is a fixed device array of TANN_STATIC_SCRATCH_BYTES inside
+ * the library. NO COUNTERPART IN THE REFERENCE. It is for callers that may not call cudaMalloc /
+ * cudaFree where they rerank (both synchronise the whole device, which stalls every other stream of a
+ * serving process) and that hold no pre-allocated work space.
+ *   - needs 256 + align256(Q*dim) [float queries on uint8 vectors] + 2*align256(Q*top_n*4) bytes;
+ *     larger batches return TANN_ERR_UNSUPPORTED with the sizes in tann_last_error();
+ *   - the first call on a device looks up the array's address with that device current: make that
+ *     call before any stream capture;
+ *   - calls that overlap on the GPU (other streams or threads) share the array and race: serialise them. */
+#define TANN_STATIC_SCRATCH_BYTES (8u << 20)
+TannStatus tann_rerank_topk_static(const TannIndexView* index, const TannRerankParams* params,
+                                   const void* candidates /*dev [Q][capacity]*/, uint32_t candidate_capacity,
+                                   uint64_t num_queries, const void* queries /*dev [Q][dim]*/,
+                                   uint32_t query_kind, const float* error_bounds /*dev [N] or NULL*/,
+                                   float* out_dists /*dev [Q][top_k]*/, uint32_t* out_ids /*dev [Q][top_k]*/,
+                                   tann_stream_t stream);
+
 /* ---- memory helpers for the providers (HBM-resident, NVLink-peer, pinned-host / UVA) -------- */
 TannStatus tann_device_alloc(uint64_t bytes, void** out_dev);
 TannStatus tann_device_free(void* dev);

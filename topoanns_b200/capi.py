@@ -103,6 +103,8 @@ SIGNATURES = {
     "tann_rerank_exact": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                _VP, _VP, _VP, _VP, _VP, _VP]),
     "tann_topk_pack": (_I, [_VP, _VP, _U64, _U32, _U32, _VP, _VP, _VP]),
+    "tann_rerank_topk_static": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
+                                     _VP, _VP, _VP, _VP]),
     "tann_device_alloc": (_I, [_U64, C.POINTER(_VP)]),
     "tann_device_free": (_I, [_VP]),
     "tann_host_alloc_mapped": (_I, [_U64, C.POINTER(_VP), C.POINTER(_VP)]),

@@ -103,6 +103,8 @@ TannStatus PlanBeam(const TannIndexView* ix, const TannBeamParams* p, bool lut_i
 }  // namespace
 
 namespace tann {
+void SetLastError(const char* message) { Fail(TANN_OK, "%s", message); }
+
 int SmCount() {
     static thread_local int cached_dev = -1, cached = 0;
     int dev = 0;
