@@ -40,6 +40,22 @@ def main():
     qn = sh.queries.cpu().numpy()
     ids, dists, stats = sr.run_host(qn[b:e], tp, rp, want_stats=True)
     all_ids, all_d = sharding.gather_topk(torch.from_numpy(ids.view(np.int32)).cuda(), torch.from_numpy(dists).cuda(), Q)
+    # throughput of the sharded search (every rank searches its query slice; (G-1)/G of the gathers are remote)
+    steps = int(os.environ.get("TANN_STEPS", "20"))
+    q_dev = sh.queries[b:e].cuda().contiguous()
+    for _ in range(3):
+        sr.run_device(q_dev, tp, rp)
+    dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(steps):
+        sr.run_device(q_dev, tp, rp)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([ev0.elapsed_time(ev1) / steps], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    sharded_ms = float(ms.item())
     whole = synth_sharded.gather_whole(sh)
     ok = True
     if rank == 0:
@@ -55,8 +71,20 @@ def main():
         same_checker = np.array_equal(got_ids, ref["topk_ids"]) and np.array_equal(got_d.view(np.uint32), ref["topk_dists"].view(np.uint32))
         rec = synth.recall_at_k(got_ids, whole.gt_ids.cpu().numpy(), 10)
         remote = 1.0 - 1.0 / world
+        q_all = sh.queries.cuda().contiguous()
+        for _ in range(3):
+            sr2.run_device(q_all, tp, rp)
+        torch.cuda.synchronize()
+        ev0.record()
+        for _ in range(steps):
+            sr2.run_device(q_all, tp, rp)
+        ev1.record()
+        torch.cuda.synchronize()
+        single_ms = ev0.elapsed_time(ev1) / steps
         print(f"sharded x{world}: nodes={sh.total_nodes} identical_to_unsharded={same_unsharded} identical_to_checker={same_checker} "
-              f"recall@10={rec:.3f} expected_remote_fraction={remote:.3f}")
+              f"recall@10={rec:.3f} expected_remote_fraction={remote:.3f} "
+              f"sharded_ms_per_batch={sharded_ms:.3f} ({Q / sharded_ms * 1e3:.0f} QPS over {world} GPUs) "
+              f"one_gpu_whole_index_ms={single_ms:.3f} ({Q / single_ms * 1e3:.0f} QPS)")
         ok = same_unsharded and same_checker
         sr2.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")

@@ -236,12 +236,12 @@ __device__ __forceinline__ float AdcTreeThread(const float* lut, const uint8_t* 
 // Query look-up table (src/search/pq_query_tables.cu:33-52), four consecutive centroids per thread
 // and step: one 16-byte load per dim and the same per-entry FMA chain (ascending dim) as the
 // one-entry form. kSub = dims per chunk when every chunk has that many: the loads of a step
-// (about eight per thread) are then all issued before the first is used, which is what keeps the
+// (sixteen per thread) are then all issued before the first is used, which is what keeps the
 // 128 KB table stream from L2 from being latency-bound.
 template <int kSub>
 __device__ __forceinline__ void BuildLutUniform(float* lut, const float* sq, const float* tables,
                                                 uint32_t M, uint32_t tid) {
-    constexpr int kItems = kSub <= 2 ? 4 : (kSub <= 4 ? 2 : 1);
+    constexpr int kItems = kSub <= 2 ? 8 : (kSub <= 4 ? 4 : 2);   // 16 loads in flight per thread
     const uint32_t total = M * (kCentroids / 4);
     for (uint32_t item0 = tid; item0 < total; item0 += kBeamThreads * kItems) {
         float4 t[kItems][kSub];
@@ -708,15 +708,27 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             }
             if (accepted != 0) {
                 const uint32_t kept = nv - accepted;
-                for (uint32_t i = tid; i < kept; i += kBeamThreads) {
-                    const unsigned long long c = cur[i];
-                    const unsigned long long ck = c & kCmpMask;
-                    uint32_t lo = 0, hi = accepted;  // frontier keys <= ck go in front of it
-                    while (lo < hi) {
-                        const uint32_t mid = (lo + hi) >> 1;
-                        if (sorted[mid] <= ck) lo = mid + 1; else hi = mid;
+                // Every kept element moves back by the number of accepted keys <= it (those go in front
+                // of it). The count is a fixed-trip binary search, two elements per thread at a time so
+                // that their shared-memory reads overlap.
+                const uint32_t top_bit = 1u << (31 - __clz(accepted));
+                for (uint32_t i0 = tid; i0 < kept; i0 += 2 * kBeamThreads) {
+                    const uint32_t i1 = i0 + kBeamThreads;
+                    const bool two = i1 < kept;
+                    const unsigned long long c0 = cur[i0];
+                    const unsigned long long c1 = two ? cur[i1] : 0ull;
+                    const unsigned long long ck0 = c0 & kCmpMask, ck1 = c1 & kCmpMask;
+                    uint32_t p0 = 0, p1 = 0;
+                    for (uint32_t b = top_bit; b > 0; b >>= 1) {
+                        const uint32_t t0 = p0 + b, t1 = p1 + b;
+                        const bool in0 = t0 <= accepted, in1 = two && t1 <= accepted;
+                        const unsigned long long s0 = in0 ? sorted[t0 - 1] : ~0ull;
+                        const unsigned long long s1 = in1 ? sorted[t1 - 1] : ~0ull;
+                        if (s0 <= ck0) p0 = t0;
+                        if (s1 <= ck1) p1 = t1;
                     }
-                    nxt[i + lo] = c;
+                    nxt[i0 + p0] = c0;
+                    if (two) nxt[i1 + p1] = c1;
                 }
                 for (uint32_t i = nv + tid; i < C; i += kBeamThreads) nxt[i] = kInvalidKey;
                 unsigned long long* t = cur; cur = nxt; nxt = t;

@@ -32,6 +32,16 @@ TannStatus CudaFail(cudaError_t e, const char* what) {
         if (e__ != cudaSuccess) return CudaFail(e__, #call); \
     } while (0)
 
+// True for host memory the driver knows as page-locked (cudaHostAlloc, cudaHostRegister).
+bool IsPageLocked(const void* p) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return attr.type == cudaMemoryTypeHost;
+}
+
 uint32_t NextPow2(uint32_t v) {
     uint32_t p = 1;
     while (p < v) p <<= 1;
@@ -564,9 +574,14 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const 
     if (query_kind > TANN_KIND_FLOAT32) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: unknown query kind.");
     if (Q == 0) return TANN_OK;
     const size_t qbytes = Q * (size_t)s->ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
-    // One pinned staging copy keeps the H2D asynchronous whatever memory the caller hands in.
-    memcpy(s->h_queries, queries_host, qbytes);
-    TANN_CUDA(cudaMemcpyAsync(s->d_queries, s->h_queries, qbytes, cudaMemcpyHostToDevice, stream));
+    // Pageable memory goes through one pinned staging copy so that the H2D stays asynchronous;
+    // page-locked memory (cudaHostAlloc / cudaHostRegister) is copied from where it is.
+    const void* h2d_src = queries_host;
+    if (!IsPageLocked(queries_host)) {
+        memcpy(s->h_queries, queries_host, qbytes);
+        h2d_src = s->h_queries;
+    }
+    TANN_CUDA(cudaMemcpyAsync(s->d_queries, h2d_src, qbytes, cudaMemcpyHostToDevice, stream));
     const uint32_t* eo = nullptr;
     const uint32_t* ei = nullptr;
     if (fixed_entries_host != nullptr && num_fixed_entries != 0) {
@@ -586,12 +601,15 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const 
                                              nullptr, nullptr, stream);
     if (st != TANN_OK) return st;
     const size_t kbytes = Q * (size_t)rerank->top_k * 4;
-    TANN_CUDA(cudaMemcpyAsync(s->h_topk_ids, s->d_topk_ids, kbytes, cudaMemcpyDeviceToHost, stream));
-    TANN_CUDA(cudaMemcpyAsync(s->h_topk_dists, s->d_topk_dists, kbytes, cudaMemcpyDeviceToHost, stream));
+    const bool ids_direct = IsPageLocked(out_ids_host), dists_direct = IsPageLocked(out_dists_host);
+    TANN_CUDA(cudaMemcpyAsync(ids_direct ? (void*)out_ids_host : (void*)s->h_topk_ids, s->d_topk_ids, kbytes,
+                              cudaMemcpyDeviceToHost, stream));
+    TANN_CUDA(cudaMemcpyAsync(dists_direct ? (void*)out_dists_host : (void*)s->h_topk_dists, s->d_topk_dists, kbytes,
+                              cudaMemcpyDeviceToHost, stream));
     if (out_stats_host) TANN_CUDA(cudaMemcpyAsync(s->h_stats, s->d_stats, Q * 32, cudaMemcpyDeviceToHost, stream));
     TANN_CUDA(cudaStreamSynchronize(stream));
-    memcpy(out_ids_host, s->h_topk_ids, kbytes);
-    memcpy(out_dists_host, s->h_topk_dists, kbytes);
+    if (!ids_direct) memcpy(out_ids_host, s->h_topk_ids, kbytes);
+    if (!dists_direct) memcpy(out_dists_host, s->h_topk_dists, kbytes);
     if (out_stats_host) memcpy(out_stats_host, s->h_stats, Q * 32);
     return TANN_OK;
 }

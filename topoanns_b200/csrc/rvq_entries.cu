@@ -114,8 +114,27 @@ rvq_entries_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t dim,
                 float dot[QB];
 #pragma unroll
                 for (int qi = 0; qi < QB; ++qi) dot[qi] = 0.0f;
-#pragma unroll 4
-                for (uint32_t k = 0; k < dim; ++k) {
+                // 16 codebook values per step are requested before the first is used (the FMA order per
+                // query stays ascending k)
+                constexpr uint32_t kAhead = 16;
+                uint32_t k0 = 0;
+                for (; k0 + kAhead <= dim; k0 += kAhead) {
+                    float w[kAhead];
+#pragma unroll
+                    for (uint32_t u = 0; u < kAhead; ++u) w[u] = __ldg(book_t + (size_t)(k0 + u) * count + c);
+#pragma unroll
+                    for (uint32_t u = 0; u < kAhead; ++u) {
+#pragma unroll
+                        for (int g = 0; g < QB / 4; ++g) {
+                            const float4 xv = *reinterpret_cast<const float4*>(x + (k0 + u) * QB + 4 * g);
+                            dot[4 * g + 0] = fmaf(xv.x, w[u], dot[4 * g + 0]);
+                            dot[4 * g + 1] = fmaf(xv.y, w[u], dot[4 * g + 1]);
+                            dot[4 * g + 2] = fmaf(xv.z, w[u], dot[4 * g + 2]);
+                            dot[4 * g + 3] = fmaf(xv.w, w[u], dot[4 * g + 3]);
+                        }
+                    }
+                }
+                for (uint32_t k = k0; k < dim; ++k) {
                     const float w = __ldg(book_t + (size_t)k * count + c);
 #pragma unroll
                     for (int g = 0; g < QB / 4; ++g) {

@@ -316,12 +316,16 @@ class Searcher:
         capi.check(capi.load().tann_searcher_set_pq2(self._h, C.byref(v)))
 
     def run_host(self, queries: np.ndarray, topology: TopologySearchParams, rerank: RerankExactParams,
-                 fixed_entries: Optional[np.ndarray] = None, want_stats: bool = False):
-        """queries: numpy [Q, dim] (float32 / uint8 / int8). Returns (ids [Q,k] u32, dists [Q,k] f32, stats)."""
+                 fixed_entries: Optional[np.ndarray] = None, want_stats: bool = False,
+                 out_ids: Optional[np.ndarray] = None, out_dists: Optional[np.ndarray] = None):
+        """queries: numpy [Q, dim] (float32 / uint8 / int8). Returns (ids [Q,k] u32, dists [Q,k] f32, stats).
+        Page-locked query / output arrays (e.g. views of torch pinned tensors) are copied without staging."""
         q = np.ascontiguousarray(queries)
         Q = q.shape[0]
-        ids = np.empty((Q, rerank.top_k), np.uint32)
-        dists = np.empty((Q, rerank.top_k), np.float32)
+        ids = out_ids if out_ids is not None else np.empty((Q, rerank.top_k), np.uint32)
+        dists = out_dists if out_dists is not None else np.empty((Q, rerank.top_k), np.float32)
+        assert ids.shape == (Q, rerank.top_k) and ids.dtype == np.uint32 and ids.flags.c_contiguous
+        assert dists.shape == (Q, rerank.top_k) and dists.dtype == np.float32 and dists.flags.c_contiguous
         stats = np.empty((Q, 8), np.uint32) if want_stats else None
         cap = topology.capacity(rerank.top_n)
         bp = topology.to_c(cap)
