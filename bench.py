@@ -30,6 +30,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+os.environ.setdefault("NCCL_DEBUG", "WARN")  # keeps NCCL's version banner off stdout: one JSON line only
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 

@@ -11,9 +11,14 @@
 // reference's own tests (tests/test_pq_query_tables.cpp:102-116,
 // tests/test_topology_search_gpu.cpp:182-221, tests/test_topology_search_batch_gpu.cpp:182-199,
 // tests/test_rerank_exact.cpp:133-145, tests/test_pq2_residual_refine.cpp:134-138,
-// tests/test_pq2_bound_filter.cpp:167-171). RVQ entry selection, the learned traversal stop and
-// Bloom false-positive behaviour have no known-answer test in the reference ("parity unpinned"
-// for those three).
+// tests/test_pq2_bound_filter.cpp:167-171), and against outputs of the reference's own kernels: the
+// reference's sources for this path compile in place (oracle/ref_build.sh) and, run on a B200, give
+// tables, candidate lists, per-query statistics, refined lists and rerank output that this file
+// reproduces bit for bit (tests/test_reference_pin.py; a small recorded case is committed as
+// tests/golden/reference_small.npz and checked on the CPU). That covers the Bloom filter's
+// false-positive behaviour and the visited-set protocol as well. Still "parity unpinned": RVQ entry
+// selection (the reference scores with a cuBLAS GEMM whose summation order is not published) and
+// the learned traversal stop (no model file or known-answer test in the reference).
 //
 // Floating point: where the reference's device code is `acc += a * b` nvcc contracts it to one
 // fused multiply-add, so the restatement calls fmaf() explicitly; this file is compiled with

@@ -280,6 +280,50 @@ def test_rerank_uint8_bit_exact_and_sorted():
         assert np.array_equal(dd.astype(np.int64), want)
 
 
+@pytest.mark.parametrize("top_n", [1, 7, 40, 100, 300, 600])
+def test_rerank_sizes_and_query_kinds(top_n):
+    """Every rerank path (8 lanes per candidate with integer, uint8-row/float-query and float rows, the
+    warp-per-candidate fallback for int8 queries) at list lengths around the sort's and tiling's
+    boundaries, bit for bit against the checker."""
+    s, host = small_index()
+    ix = device_index(s)
+    Q = s.queries.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid])
+    L = max(64, min(top_n, 512))
+    p = search.TopologySearchParams(top_l=L, search_width=2, max_expansions=4096)
+    q_f32 = s.queries.cuda().contiguous()
+    cand, _ = search.beam_search(ix, p, eo, ei, queries=q_f32, capacity=p.capacity(top_n))
+    rp = search.RerankExactParams(top_k=min(10, top_n), top_n=top_n)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q_frac = (q_f32 + torch.rand(q_f32.shape, generator=g, device="cuda") * 0.75).contiguous()   # not uint8-valued
+    q_i8 = (q_f32 / 2).to(torch.int8).contiguous()
+    for qt in (q_f32.to(torch.uint8).contiguous(), q_f32, q_frac, q_i8):
+        d, i, n_exact, _ = search.rerank_exact(ix, rp, cand, qt)
+        rd, ri, rn, _ = orc.rerank(np_u32(cand), qt.cpu().numpy(), host_pages(host), np.uint8, top_n=top_n,
+                                   top_k=rp.top_k, vectors_per_page=host["vpp"], page_bytes=4096, vector_bytes=host["vb"])
+        assert n_exact == rn
+        assert np.array_equal(np_u32(i), ri), str(qt.dtype)
+        assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32)), str(qt.dtype)
+
+
+@pytest.mark.parametrize("top_n", [5, 64, 200])
+def test_rerank_float_rows(top_n):
+    s, host = small_index(name="cfg3", num_nodes=12000, components=60, num_queries=128)
+    ix = device_index(s)
+    Q = s.queries.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid])
+    p = search.TopologySearchParams(top_l=max(64, top_n), search_width=2, max_expansions=4096)
+    q = s.queries.cuda().contiguous()
+    cand, _ = search.beam_search(ix, p, eo, ei, queries=q, capacity=p.capacity(top_n))
+    rp = search.RerankExactParams(top_k=min(10, top_n), top_n=top_n)
+    d, i, n_exact, _ = search.rerank_exact(ix, rp, cand, q)
+    rd, ri, rn, _ = orc.rerank(np_u32(cand), q.cpu().numpy(), host_pages(host), np.float32, top_n=top_n, top_k=rp.top_k,
+                               vectors_per_page=host["vpp"], page_bytes=4096, vector_bytes=host["vb"])
+    assert n_exact == rn
+    assert np.array_equal(np_u32(i), ri)
+    assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
+
+
 def host_pages(host):
     if host.get("pages") is None:
         pages, vpp, vb = pipeline.vectors_to_pages(host["vectors"])

@@ -23,7 +23,7 @@
 #include "tann_launch.h"
 
 // Optional per-phase cycle counters (development builds only: -DTANN_BEAM_PROFILE). Thread 0 adds
-// clock64() deltas per phase into a [Q][8] uint64 array passed through BeamArgs::status.
+// clock64() deltas per phase into a [Q][12] uint64 array passed through BeamArgs::status.
 #ifdef TANN_BEAM_PROFILE
 #define TANN_PHASE(i)                                            \
     do {                                                         \
@@ -77,10 +77,26 @@ __device__ __forceinline__ uint32_t FindFirstSetBit(const uint32_t* bits, uint32
     return limit;
 }
 
+// Position of set bit number n (0-based) in a bitmap of up to four words; n must be below its popcount.
+__device__ __forceinline__ uint32_t NthSetBit(const uint32_t (&wd)[4], uint32_t n) {
+    uint32_t word = wd[0], base = 0;
+    const uint32_t c0 = __popc(wd[0]), c1 = __popc(wd[1]), c2 = __popc(wd[2]);
+    if (n >= c0) {
+        n -= c0; word = wd[1]; base = 32;
+        if (n >= c1) {
+            n -= c1; word = wd[2]; base = 64;
+            if (n >= c2) { n -= c2; word = wd[3]; base = 96; }
+        }
+    }
+    for (uint32_t i = 0; i < n; ++i) word &= word - 1u;
+    return base + __ffs(word) - 1;
+}
+
 // Sets the expanded flag of the list elements this lane picked (the picks sel_begin..sel_end-1 are
 // the lowest set bits of its bitmap word). Runs on warp 0 once every warp has read the ids.
 __device__ __forceinline__ void MarkExpanded(unsigned long long* cur, uint32_t word, uint32_t sel_begin,
-                                             uint32_t sel_end, uint32_t lane) {
+                                             uint32_t sel_end, uint32_t lane, uint32_t mark_pos) {
+    if (mark_pos != kInvalid) cur[mark_pos] |= kExpandedBit;
     for (uint32_t sidx = sel_begin; sidx < sel_end; ++sidx) {
         const uint32_t bit = __ffs(word) - 1;
         word &= word - 1u;
@@ -293,22 +309,6 @@ __device__ __noinline__ void BuildLutGeneric(float* lut, const float* sq, const 
     }
 }
 
-// Bitonic sort of one key per lane across a warp, ascending by lane.
-__device__ __forceinline__ unsigned long long WarpSortKey(unsigned long long k, uint32_t lane) {
-#pragma unroll
-    for (uint32_t size = 2; size <= 32; size <<= 1) {
-#pragma unroll
-        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
-            const unsigned long long o = __shfl_xor_sync(kFull, k, stride);
-            const bool upper = (lane & stride) != 0;          // this lane holds the pair's upper slot
-            const bool asc = (lane & size) == 0 || size == 32;
-            const bool take_min = upper != asc;
-            k = take_min ? (o < k ? o : k) : (o > k ? o : k);
-        }
-    }
-    return k;
-}
-
 // Bitonic sort of F keys held in shared memory (any power of two F).
 __device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
     for (uint32_t k = 2; k <= F; k <<= 1) {
@@ -358,6 +358,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
     __shared__ uint32_t s_sel[kBeamThreads / 32][TANN_MAX_SEARCH_WIDTH];  // selected nodes, one copy per warp
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31;
+    const uint32_t my_k = deg ? tid / deg : 0u, my_j = tid - my_k * deg;  // slot of this thread (kSingle)
 
     // Chunks of equal width (the usual case) take the unrolled table build.
     uint32_t uniform_sub = 0;
@@ -371,7 +372,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
     for (uint64_t q = blockIdx.x; q < a.num_queries; q += gridDim.x) {
 #ifdef TANN_BEAM_PROFILE
-        unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        unsigned long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
         long long prof_t = clock64();
 #endif
         // ---- per-query set-up --------------------------------------------------------------
@@ -426,6 +427,8 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         while (true) {
             uint32_t nslots;
             uint32_t sel_word = 0, sel_begin = 0, sel_end = 0;  // this lane's share of the selection
+            uint32_t mark_pos = kInvalid;   // list rank this lane marks as expanded (bitmaps of <= 4 words)
+            uint32_t my_node = kInvalid;    // kSingle, bitmaps of <= 4 words: the node of this thread's slot
             if (in_entries) {
                 nslots = slots;
             } else {
@@ -446,7 +449,42 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 }
                 if (!stop) {
                     const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
-                    if (UW <= 32) {
+                    if (UW <= 4) {
+                        // up to 128 list ranks: every thread reads the whole bitmap and finds the
+                        // pick of its own slot directly (no scan, no exchange)
+                        uint32_t wd[4];
+#pragma unroll
+                        for (uint32_t u = 0; u < 4; ++u) wd[u] = u < UW ? unexp[u] : 0u;
+                        bool any;
+                        if (prefix_stop && a.p.stop_use_expanded) {
+                            any = !(valid >= L && expanded >= a.p.stop_prefix);
+                        } else {
+                            const uint32_t words = (prefix_stop && valid >= a.p.stop_prefix)
+                                                       ? (a.p.stop_prefix + 31) / 32 : UW;
+                            uint32_t acc = 0;
+#pragma unroll
+                            for (uint32_t u = 0; u < 4; ++u) acc |= u < words ? wd[u] : 0u;
+                            any = acc != 0u;
+                        }
+                        if (!any) {
+                            stop = 2;
+                        } else {
+                            nsel = min((uint32_t)(__popc(wd[0]) + __popc(wd[1]) + __popc(wd[2]) + __popc(wd[3])), W);
+                            if (nsel == 0) {
+                                stop = 1;
+                            } else if (kSingle) {
+                                if (my_k < nsel) my_node = KeyPackedId(cur[NthSetBit(wd, my_k)]) & kRawMask;
+                                if (tid < nsel) mark_pos = NthSetBit(wd, tid);   // warp 0 marks them later
+                            } else {
+                                if (lane < nsel) {
+                                    const uint32_t pos = NthSetBit(wd, lane);
+                                    s_sel[tid >> 5][lane] = KeyPackedId(cur[pos]) & kRawMask;
+                                    if (tid < 32) mark_pos = pos;
+                                }
+                                __syncwarp();
+                            }
+                        }
+                    } else if (UW <= 32) {
                         sel_word = lane < UW ? unexp[lane] : 0u;
                         bool any;
                         if (prefix_stop && a.p.stop_use_expanded) {
@@ -531,7 +569,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             const uint32_t rounds = kSingle ? 1u : (nslots + kBeamThreads - 1) / kBeamThreads;
             if (!kSingle) {
                 __syncthreads();
-                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane);
+                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane, mark_pos);
             }
             for (uint32_t r = 0; r < rounds; ++r) {
                 const uint32_t s = r * kBeamThreads + tid;
@@ -541,8 +579,9 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         const uint64_t e = (uint64_t)batch * slots + s;
                         if (e < num_entries) id = __ldg(a.entry_ids + entry_begin + e);
                     } else {
-                        const uint32_t k = s / deg, j = s - k * deg;
-                        const uint32_t node = s_sel[tid >> 5][k];
+                        uint32_t k, j, node;
+                        if (kSingle) { k = my_k; j = my_j; } else { k = s / deg; j = s - k * deg; }
+                        if (kSingle && UW <= 4) node = my_node; else node = s_sel[tid >> 5][k];
                         const uint32_t* row =
                             (node < a.ix.adjacency_cached_rows)
                                 ? a.ix.adjacency_cache + (uint64_t)node * deg
@@ -573,7 +612,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             }
             if (kSingle) {
                 __syncthreads();  // every test of the round precedes every add
-                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane);
+                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane, mark_pos);
             }
             TANN_PHASE(2);  // 2: slot ids (adjacency / entries) + Bloom tests
             // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
@@ -624,6 +663,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 base = __shfl_sync(kFull, base, 0);
                 if (surv) fkey[base + __popc(ballot & ((1u << lane) - 1u))] = my_key;
                 __syncthreads();
+                TANN_PHASE(8);  // 8: filter + compaction (waits for every code row)
                 const uint32_t n = s_surv;
                 fv = s_pass;
                 nv = (uint32_t)min((uint64_t)C, (uint64_t)valid + fv);
@@ -640,36 +680,55 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     __syncthreads();
                     rank = lane;
                     const uint32_t w = tid >> 5;
+                    uint32_t cnt[kBeamThreads / 32];
 #pragma unroll
-                    for (uint32_t o = 0; o < kBeamThreads / 32; ++o) {
-                        if (o == w) continue;
-                        const unsigned long long* run = fkey + o * 32;
-                        uint32_t lo = 0, hi = 32;
-                        while (lo < hi) {
-                            const uint32_t mid = (lo + hi) >> 1;
-                            const unsigned long long x = run[mid];
-                            if (o < w ? x <= k : x < k) lo = mid + 1; else hi = mid;
+                    for (uint32_t o = 0; o < kBeamThreads / 32; ++o) cnt[o] = 0;
+#pragma unroll
+                    for (uint32_t b = 32; b > 0; b >>= 1) {       // the searches of the other runs, side by side
+#pragma unroll
+                        for (uint32_t o = 0; o < kBeamThreads / 32; ++o) {
+                            const uint32_t t = cnt[o] + b;
+                            if (o != w && t <= 32) {
+                                const unsigned long long x = fkey[o * 32 + t - 1];
+                                if (o < w ? x <= k : x < k) cnt[o] = t;
+                            }
                         }
-                        rank += lo;
                     }
+#pragma unroll
+                    for (uint32_t o = 0; o < kBeamThreads / 32; ++o) rank += cnt[o];
                 } else if (tid < n) {
                     k = fkey[tid];
+#pragma unroll 8
                     for (uint32_t j = 0; j < n; ++j) {
                         const unsigned long long kj = fkey[j];
                         rank += (kj < k || (kj == k && j < tid)) ? 1u : 0u;
                     }
                 }
+                TANN_PHASE(9);  // 9: ranks of the survivors
                 if (k != kInvalidKey) {
                     skey[rank] = k;
                     if (rank < nv) pred = k < (cur[nv - 1 - rank] & kCmpMask);
                     if (pred) {
-                        uint32_t lo = 0, hi = valid;  // list elements < k stay in front of it
-                        while (lo < hi) {
-                            const uint32_t mid = (lo + hi) >> 1;
-                            if ((cur[mid] & kCmpMask) < k) lo = mid + 1; else hi = mid;
+                        uint32_t lo = 0;  // list elements < k stay in front of it (fixed-trip count)
+                        if (valid != 0) {
+                            for (uint32_t b = 1u << (31 - __clz(valid)); b > 0; b >>= 1) {
+                                const uint32_t t = lo + b;
+                                if (t <= valid && (cur[t - 1] & kCmpMask) < k) lo = t;
+                            }
                         }
                         nxt[rank + lo] = k;
                         if (rank + lo < a.p.learned_stop.top_k) ctl.ls_topk_changed = 1;
+                        // An entry that lands inside the top L will most likely be expanded within the
+                        // next pushes: ask L2 for its adjacency row now (a hint, results do not depend
+                        // on it), so that the selection's load does not wait for DRAM.
+                        if (rank + lo < L && a.adjacency_in_local_hbm) {
+                            const uint32_t node = (uint32_t)k;
+                            if (node >= a.ix.adjacency_cached_rows) {
+                                const uint8_t* row = static_cast<const uint8_t*>(a.ix.adjacency.base[0]) + (uint64_t)node * deg * 4;
+                                for (uint32_t off = 0; off < deg * 4; off += 128)
+                                    asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
+                            }
+                        }
                     }
                 }
                 accepted = __syncthreads_count(pred);
@@ -787,8 +846,8 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         TANN_PHASE(7);  // 7: output
 #ifdef TANN_BEAM_PROFILE
         if (tid == 0 && a.status != nullptr) {
-            unsigned long long* o = reinterpret_cast<unsigned long long*>(a.status) + q * 8;
-            for (int i = 0; i < 8; ++i) o[i] = prof_acc[i];
+            unsigned long long* o = reinterpret_cast<unsigned long long*>(a.status) + q * 12;
+            for (int i = 0; i < 12; ++i) o[i] = prof_acc[i];
         }
 #endif
     }

@@ -368,8 +368,19 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                 __syncthreads();
             }
         }
-        // final sort and output
-        for (uint32_t k = 2; k <= padded; k <<= 1) {
+        // final sort and output: bitonic network; the stages inside runs of 32 keys are done by one
+        // warp per run with shuffles (no barriers), the wider stages in shared memory
+        uint32_t first_k = 2;
+        if (padded >= 64) {
+            for (uint32_t c = warp; c < padded / 32; c += kRerankThreads / 32) {
+                unsigned long long k = WarpSortKey(keys[c * 32 + lane], lane);
+                if (c & 1u) k = __shfl_sync(kFull, k, 31 - lane);   // odd runs descending, as the network expects
+                keys[c * 32 + lane] = k;
+            }
+            __syncthreads();
+            first_k = 64;
+        }
+        for (uint32_t k = first_k; k <= padded; k <<= 1) {
             for (uint32_t j = k >> 1; j > 0; j >>= 1) {
                 for (uint32_t t = tid; t < padded / 2; t += kRerankThreads) {
                     const uint32_t lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));

@@ -94,6 +94,22 @@ __device__ __forceinline__ float WarpTreeSum(float v) {
     return v;
 }
 
+// Bitonic sort of one key per lane across a warp, ascending by lane.
+__device__ __forceinline__ unsigned long long WarpSortKey(unsigned long long k, uint32_t lane) {
+#pragma unroll
+    for (uint32_t size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(kFull, k, stride);
+            const bool upper = (lane & stride) != 0;          // this lane holds the pair's upper slot
+            const bool asc = (lane & size) == 0 || size == 32;
+            const bool take_min = upper != asc;
+            k = take_min ? (o < k ? o : k) : (o > k ? o : k);
+        }
+    }
+    return k;
+}
+
 template <typename T>
 __device__ __forceinline__ float LoadAsFloat(const void* p, uint32_t kind, uint64_t i) {
     if (kind == TANN_KIND_FLOAT32) return static_cast<const float*>(p)[i];
