@@ -278,11 +278,8 @@ def main():
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
+        # every rank serves its own batch and reads its own results back: no data-path collective
         ids, dists, _ = sr.run_host(q_np, tp, rp, out_ids=out_ids_np, out_dists=out_dists_np)
-        if world > 1:  # the one collective of the path: final top-k lists to rank 0
-            from topoanns_b200 import sharding
-            sharding.gather_topk(torch.from_numpy(ids.view(np.int32)).to(device), torch.from_numpy(dists).to(device),
-                                 Q * world)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()

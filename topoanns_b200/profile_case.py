@@ -15,15 +15,17 @@ from . import search, synth
 
 
 def _time(fn, reps):
+    """One warm-up call, then `reps` calls back to back between two CUDA events (the queue stays full, so
+    the host's launch latency is not part of the figure); returns (last result, mean ms per call)."""
+    out = fn()
+    torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    out = None
+    start.record()
     for _ in range(reps):
-        torch.cuda.synchronize()
-        start.record()
         out = fn()
-        stop.record()
-        torch.cuda.synchronize()
-    return out, start.elapsed_time(stop)
+    stop.record()
+    torch.cuda.synchronize()
+    return out, start.elapsed_time(stop) / reps
 
 
 def main() -> None:
@@ -35,7 +37,7 @@ def main() -> None:
     ap.add_argument("--search-width", type=int, default=2)
     ap.add_argument("--top-n", type=int, default=32)
     ap.add_argument("--entries", type=int, default=128)
-    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--staged-table", action="store_true", help="build the query tables with tann_lut_build first")
     a = ap.parse_args()
     cfg = dataclasses.replace(synth.CONFIGS[a.config], num_nodes=a.nodes, components=max(1, a.nodes // 1000),
