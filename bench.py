@@ -36,7 +36,7 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 L_SWEEP = (16, 32, 64, 128, 256, 512, 1024)
-TOPN_SWEEP = (32, 128, 256, 512)
+TOPN_SWEEP = (32, 128, 192, 256, 512)
 DEFAULT_POINT = (16, 256)   # (top_l, rerank_top_n): fastest sweep point with recall@10 >= 0.95 on the seeded cfg2 data
 # DRAM traffic of one beam_search_kernel launch (10 k queries, 10 M nodes), ncu dram__bytes_read.sum +
 # dram__bytes_write.sum, per operating point; summarised under profiles/.

@@ -561,7 +561,8 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
                                              s->d_not_u8, stream));
         if (rerank->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
         TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
-                                     s->d_ids, nullptr, stream, s->d_queries_u8, s->d_not_u8));
+                                     s->d_ids, nullptr, stream, s->d_queries_u8, s->d_not_u8,
+                                     /*only the first top_k ranks are packed below*/ rerank->top_k <= 32 ? rerank->top_k : 0));
     } else {
         st = tann_rerank_exact(&s->ix, rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
                                s->d_ids, nullptr, nullptr, stream);

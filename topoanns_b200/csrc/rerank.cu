@@ -198,7 +198,8 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
               uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
               const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
               uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts,
-              const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag) {
+              const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag,
+              uint32_t final_ranks) {
     extern __shared__ __align__(16) unsigned char rr_smem[];
     // keys[r] first holds the address of candidate r's vector (or the invalid key when the rank is
     // empty or filtered), then its (distance, id) sort key.
@@ -371,7 +372,34 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
         // final sort and output: bitonic network; the stages inside runs of 32 keys are done by one
         // warp per run with shuffles (no barriers), the wider stages in shared memory
         uint32_t first_k = 2;
-        if (padded >= 64) {
+        uint32_t out_n = p.top_n;
+        if (final_ranks != 0 && final_ranks <= 32 && padded >= 64) {
+            // The caller consumes only the first final_ranks <= 32 entries: sort every run of 32 keys,
+            // then a tournament keeps the 32 smallest of two runs (element-wise minimum of one run and
+            // the other reversed is a bitonic sequence of exactly those) and re-sorts them with five
+            // shuffle stages, halving the number of runs per round.
+            const uint32_t runs = padded / 32;
+            for (uint32_t c = warp; c < runs; c += kRerankThreads / 32)
+                keys[c * 32 + lane] = WarpSortKey(keys[c * 32 + lane], lane);
+            __syncthreads();
+            for (uint32_t stride = 1; stride < runs; stride <<= 1) {
+                for (uint32_t a = warp * 2 * stride; a + stride < runs; a += (kRerankThreads / 32) * 2 * stride) {
+                    const unsigned long long ka = keys[a * 32 + lane];
+                    const unsigned long long kb = keys[(a + stride) * 32 + (31 - lane)];
+                    unsigned long long m = ka < kb ? ka : kb;
+#pragma unroll
+                    for (uint32_t sft = 16; sft > 0; sft >>= 1) {
+                        const unsigned long long o = __shfl_xor_sync(kFull, m, sft);
+                        const bool upper = (lane & sft) != 0;
+                        m = upper ? (o > m ? o : m) : (o < m ? o : m);
+                    }
+                    keys[a * 32 + lane] = m;
+                }
+                __syncthreads();
+            }
+            first_k = padded * 2;   // skips the network below
+            out_n = min(p.top_n, 32u);
+        } else if (padded >= 64) {
             for (uint32_t c = warp; c < padded / 32; c += kRerankThreads / 32) {
                 unsigned long long k = WarpSortKey(keys[c * 32 + lane], lane);
                 if (c & 1u) k = __shfl_sync(kFull, k, 31 - lane);   // odd runs descending, as the network expects
@@ -392,7 +420,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                 __syncthreads();
             }
         }
-        for (uint32_t i = tid; i < p.top_n; i += kRerankThreads) {
+        for (uint32_t i = tid; i < out_n; i += kRerankThreads) {
             const unsigned long long k = keys[i];
             out_dists[q * p.top_n + i] = FromOrderedBits((uint32_t)(k >> 32));
             out_ids[q * p.top_n + i] = (uint32_t)k;
@@ -424,7 +452,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
                          uint32_t capacity, uint64_t Q, const void* queries, uint32_t query_kind,
                          const float* error_bounds, float* out_dists, uint32_t* out_ids,
                          unsigned long long* out_counts, cudaStream_t stream, const uint8_t* queries_u8,
-                         const uint32_t* not_u8_flag) {
+                         const uint32_t* not_u8_flag, uint32_t final_ranks) {
     if (Q == 0 || p.top_n == 0) return cudaSuccess;
     uint32_t padded = 1;
     while (padded < p.top_n) padded <<= 1;
@@ -438,7 +466,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     const uint64_t cap = (uint64_t)SmCount() * 8;
     rerank_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, static_cast<const Cand*>(cand), capacity, Q, queries, query_kind, error_bounds, padded,
-        out_dists, out_ids, out_counts, queries_u8, not_u8_flag);
+        out_dists, out_ids, out_counts, queries_u8, not_u8_flag, final_ranks);
     return cudaGetLastError();
 }
 

@@ -481,17 +481,19 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
                     }
                 }
             }
+            if ((int)(qg * 8) < nq) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                ArgMin v = best[j];
+                for (int j = 0; j < 8; ++j) {
+                    ArgMin v = best[j];
 #pragma unroll
-                for (int off = 16; off >= 1; off >>= 1) {
-                    ArgMin o;
-                    o.d = __shfl_xor_sync(kFull, v.d, off);
-                    o.idx = __shfl_xor_sync(kFull, v.idx, off);
-                    v = Better(v, o);
+                    for (int off = 16; off >= 1; off >>= 1) {
+                        ArgMin o;
+                        o.d = __shfl_xor_sync(kFull, v.d, off);
+                        o.idx = __shfl_xor_sync(kFull, v.idx, off);
+                        v = Better(v, o);
+                    }
+                    if (lane == 0) scratch[warp][j] = v;
                 }
-                if (lane == 0) scratch[warp][j] = v;
             }
             __syncthreads();
             if ((int)tid < nq) {
@@ -505,19 +507,20 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
     }
     __syncthreads();
     // gather, rvq_device_entries.cu:15-52
-#pragma unroll 4
-    for (uint64_t e = tid; e < (uint64_t)n_mine * entry_count; e += kSmemThreads) {
-        const uint32_t qi = (uint32_t)(e / entry_count), i = (uint32_t)(e - (uint64_t)qi * entry_count);
+    for (uint32_t qi = warp; qi < n_mine; qi += kWarps) {   // one warp per query: no index division
         const int cluster = best_cluster[qi];
         uint32_t begin = 0, n = 0;
         if (cluster >= 0) {
             begin = cluster_offsets[cluster];
             n = min(cluster_offsets[cluster + 1] - begin, entry_count);
         }
-        uint32_t v = kInvalid;
-        if (i < n) v = cluster_ids[begin + i];
-        else if (n == 0 && i == 0) v = fallback;
-        out_entry_ids[(q_begin + qi) * entry_count + i] = v;
+        uint32_t* o = out_entry_ids + (q_begin + qi) * entry_count;
+        for (uint32_t i = lane; i < entry_count; i += 32) {
+            uint32_t v = kInvalid;
+            if (i < n) v = cluster_ids[begin + i];
+            else if (n == 0 && i == 0) v = fallback;
+            o[i] = v;
+        }
     }
     if (out_clusters != nullptr)
         for (uint32_t qi = tid; qi < n_mine; qi += kSmemThreads) out_clusters[q_begin + qi] = best_cluster[qi];
