@@ -351,7 +351,7 @@ def main():
         "gpu_launches": 5 * args.steps,  # rvq, beam, float->uint8 check, rerank, top-k pack
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": traffic, "peak_source": peak_src, "kernel": "beam_search_kernel",
+                     "frac_of_nominal_8tbs": achieved / 8000.0, "traffic": traffic, "peak_source": peak_src, "kernel": "beam_search_kernel",
                      "whole_step_gbs": (beam_bytes + rerank_bytes) * args.steps / (dev_ms * 1e-3) / 1e9},
     }
     if world == 1 and not args.no_cpu_baseline:

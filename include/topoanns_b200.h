@@ -204,8 +204,16 @@ TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks,
 typedef struct TannRerankParams {
     uint32_t top_n;           /* ranks [0, top_n) of each candidate list are scored */
     uint32_t top_k;
-    uint32_t tile;            /* rank tile for the bound filter; 0 = one tile */
+    uint32_t tile;            /* rank tile for the bound filter and the early stop; 0 = one tile */
     uint32_t use_bound_filter;
+    /* Early stop of the reference's persistent rerank (src/io/bam_vector_provider.cu:1124-1135): after a
+     * tile that ends at rank >= early_stop_min_prefix, with a finite k-th best exact distance, a tile
+     * that does not improve the k-th distance counts as stable (an improving one resets the count);
+     * early_stop_patience_tiles stable tiles end the query's rerank, later ranks are not scored. */
+    uint32_t use_early_stop;
+    uint32_t early_stop_min_prefix;
+    uint32_t early_stop_patience_tiles;
+    uint32_t reserved;
 } TannRerankParams;
 
 /*

@@ -190,8 +190,9 @@ def exact_distance(query, vec):
 
 
 def rerank(cand, queries, vector_pages, vec_dtype, *, top_n, top_k, tile=0, vectors_per_page,
-           page_bytes, vector_bytes, error_bounds=None):
-    """Returns (dists [Q, top_n] f32, ids [Q, top_n] u32, n_exact, n_filtered)."""
+           page_bytes, vector_bytes, error_bounds=None, early_stop_min_prefix=0, early_stop_patience_tiles=0):
+    """Returns (dists [Q, top_n] f32, ids [Q, top_n] u32, n_exact, n_filtered).
+    early_stop_patience_tiles > 0 switches the persistent rerank's early stop on."""
     cand = _c(cand, np.uint32)
     Q, capacity, _ = cand.shape
     queries = np.ascontiguousarray(queries)
@@ -206,7 +207,8 @@ def rerank(cand, queries, vector_pages, vec_dtype, *, top_n, top_k, tile=0, vect
                      C.c_uint64(vectors_per_page), C.c_uint64(page_bytes), C.c_uint64(vector_bytes),
                      1 if error_bounds is not None else 0,
                      _p(_c(error_bounds, np.float32)) if error_bounds is not None else None,
-                     _p(dists), _p(ids), _p(counts))
+                     _p(dists), _p(ids), _p(counts), C.c_uint32(early_stop_min_prefix),
+                     C.c_uint32(early_stop_patience_tiles))
     return dists, ids, int(counts[0]), int(counts[1])
 
 

@@ -30,7 +30,7 @@ def vectors_to_pages(vectors: np.ndarray, page_bytes: int = 4096):
 
 def run(index: dict, queries: np.ndarray, *, top_l, search_width, max_expansions, top_n, top_k,
         entry_count=0, fixed_entries=None, use_pq2=False, refine_top_l=0, bound_filter=False, tile=0,
-        learned_stop=None, two_phase=True, timings=None):
+        learned_stop=None, two_phase=True, timings=None, early_stop=None):
     """index: dict with adjacency [N,deg] u32, codes [N,M] u8, pq_tables [256,d], pq_centroid,
     pq_chunk_offsets, vectors [N,d], and optionally rvq_* / pq2_* arrays. Returns a dict."""
     t0 = time.perf_counter()
@@ -69,7 +69,9 @@ def run(index: dict, queries: np.ndarray, *, top_l, search_width, max_expansions
         index["pages"], index["vpp"], index["vb"] = pages, vpp, vb
     dists, ids, n_exact, n_filt = orc.rerank(src, queries, pages, index["vectors"].dtype, top_n=top_n,
                                              top_k=top_k, tile=tile, vectors_per_page=index["vpp"],
-                                             page_bytes=4096, vector_bytes=index["vb"], error_bounds=err)
+                                             page_bytes=4096, vector_bytes=index["vb"], error_bounds=err,
+                                             early_stop_min_prefix=early_stop[0] if early_stop else 0,
+                                             early_stop_patience_tiles=early_stop[1] if early_stop else 0)
     t4 = time.perf_counter()
     if timings is not None:
         timings.update(entries=t1 - t0, lut=t2 - t1, beam=t3 - t2, rerank=t4 - t3, total=t4 - t0)

@@ -681,7 +681,12 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
                 uint32_t tile, const void* queries, int query_kind, uint32_t d,
                 const uint8_t* vector_pages, int vec_kind, uint64_t vectors_per_page,
                 uint64_t page_bytes, uint64_t vector_bytes, int use_bound_filter,
-                const float* error_bounds, float* out_dists, uint32_t* out_ids, uint64_t* counts) {
+                const float* error_bounds, float* out_dists, uint32_t* out_ids, uint64_t* counts,
+                uint32_t early_stop_min_prefix, uint32_t early_stop_patience_tiles) {
+    // early_stop_patience_tiles == 0: no early stop. Otherwise the rule of the reference's persistent
+    // rerank, src/io/bam_vector_provider.cu:852-975 (tile loop, k-th distance before / after the tile)
+    // and :1124-1135 (stable-tile count).
+    const bool early = early_stop_patience_tiles != 0;
     const Cand* in = static_cast<const Cand*>(cand_in);
     const uint64_t qbytes = (uint64_t)d * (query_kind == 2 ? 4 : 1);
     uint64_t n_exact = 0, n_filtered = 0;
@@ -701,6 +706,8 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
         std::vector<float> fd(top_n, std::numeric_limits<float>::infinity());
         std::vector<uint32_t> fi(top_n, kInvalid);
         float threshold = std::numeric_limits<float>::infinity();
+        float previous_kth = std::numeric_limits<float>::infinity();
+        uint32_t stable_tiles = 0;
         for (uint32_t rb = 0; rb < top_n; rb += tile) {
             const uint32_t rc = std::min(tile, top_n - rb);
             for (uint32_t r = rb; r < rb + rc; ++r) {
@@ -717,7 +724,7 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
                 fi[r] = id;
                 ++n_exact;
             }
-            if (use_bound_filter) {  // :541-571
+            if (use_bound_filter || early) {  // :541-571
                 std::vector<float> best(top_k, std::numeric_limits<float>::infinity());
                 const uint32_t prefix = std::min(top_n, rb + rc);
                 for (uint32_t r = 0; r < prefix; ++r) {
@@ -727,7 +734,17 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
                     while (ins > 0 && x < best[ins - 1]) { best[ins] = best[ins - 1]; --ins; }
                     best[ins] = x;
                 }
-                threshold = best[top_k - 1];
+                const float kth = best[top_k - 1];
+                if (use_bound_filter) threshold = kth;
+                if (early) {
+                    bool stop = false;
+                    if (rb + rc >= early_stop_min_prefix && std::isfinite(kth)) {
+                        if (kth < previous_kth) stable_tiles = 0; else ++stable_tiles;
+                        stop = stable_tiles >= early_stop_patience_tiles;
+                    }
+                    previous_kth = kth;
+                    if (stop) break;
+                }
             }
         }
         std::vector<uint32_t> order(top_n);

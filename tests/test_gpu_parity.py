@@ -324,6 +324,38 @@ def test_rerank_float_rows(top_n):
     assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
 
 
+@pytest.mark.parametrize("min_prefix,patience", [(32, 1), (16, 2), (64, 3)])
+def test_rerank_early_stop_matches_checker(min_prefix, patience):
+    """Early stop of the persistent rerank: same scored prefix, same lists and the same count of exact
+    distances as the checker; fewer distances than without the stop."""
+    s, host = small_index()
+    ix = device_index(s)
+    Q = s.queries.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid])
+    top_n = 160
+    p = search.TopologySearchParams(top_l=top_n, search_width=2, max_expansions=4096)
+    q = s.queries.cuda().to(torch.uint8).contiguous()
+    cand, _ = search.beam_search(ix, p, eo, ei, queries=q, capacity=p.capacity(top_n))
+    rp = search.RerankExactParams(top_k=10, top_n=top_n, rank_tile_size=16, use_early_stop=True,
+                                  early_stop_min_prefix=min_prefix, early_stop_patience_tiles=patience)
+    d, i, n_exact, _ = search.rerank_exact(ix, rp, cand, q)
+    rd, ri, rn, _ = orc.rerank(np_u32(cand), q.cpu().numpy(), host_pages(host), np.uint8, top_n=top_n, top_k=10, tile=16,
+                               vectors_per_page=host["vpp"], page_bytes=4096, vector_bytes=host["vb"],
+                               early_stop_min_prefix=min_prefix, early_stop_patience_tiles=patience)
+    assert n_exact == rn
+    assert np.array_equal(np_u32(i), ri)
+    assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
+    full = search.RerankExactParams(top_k=10, top_n=top_n, rank_tile_size=16)
+    _, _, n_full, _ = search.rerank_exact(ix, full, cand, q)
+    assert n_exact < n_full
+    # a stop that can never trigger changes nothing
+    never = search.RerankExactParams(top_k=10, top_n=top_n, rank_tile_size=16, use_early_stop=True,
+                                     early_stop_min_prefix=10 ** 6, early_stop_patience_tiles=1)
+    d2, i2, n2, _ = search.rerank_exact(ix, never, cand, q)
+    d3, i3, _, _ = search.rerank_exact(ix, full, cand, q)
+    assert n2 == n_full and torch.equal(d2, d3) and torch.equal(i2, i3)
+
+
 def host_pages(host):
     if host.get("pages") is None:
         pages, vpp, vb = pipeline.vectors_to_pages(host["vectors"])
@@ -445,7 +477,8 @@ def test_sharded_and_cached_providers_give_the_same_result():
     hp, dp = C.c_void_p(), C.c_void_p()
     capi.check(lib.tann_host_alloc_mapped(nbytes, C.byref(hp), C.byref(dp)))
     try:
-        C.memmove(hp.value, ix.adjacency.cpu().numpy().ctypes.data, nbytes)
+        adj_host = ix.adjacency.cpu().numpy()   # keep the array alive across the copy
+        C.memmove(hp.value, adj_host.ctypes.data, nbytes)
         for cached_rows in (0, ix.num_nodes // 3):
             hosted = search.DeviceIndex(
                 num_nodes=ix.num_nodes, degree=ix.degree, dim=ix.dim, vector_kind=ix.vector_kind, codes=ix.codes,

@@ -172,3 +172,30 @@ def test_uint8_exact_distance_is_integer_exact(orc):
     a = np.zeros(128, np.uint8)
     b = np.full(128, 255, np.uint8)
     assert orc.exact_distance(a, b) == 128 * 255.0 ** 2
+
+
+def test_rerank_early_stop_rule(orc):
+    """The persistent rerank's early stop (src/io/bam_vector_provider.cu:1124-1135) on a hand-made case:
+    tiles of 2 ranks, k = 1; the best distance stops improving after the second tile, so with
+    min_prefix = 2 and patience 1 the third tile ends the rerank and ranks 6.. are never scored."""
+    import numpy as np
+    d = 4
+    # vector i = (dist_i, 0, 0, 0) against the zero query: squared distances below, in candidate rank order
+    sq = np.array([9, 16, 4, 25, 36, 49, 1, 64], np.float32)
+    vectors = np.zeros((8, d), np.float32)
+    vectors[:, 0] = np.sqrt(sq)
+    from oracle import pipeline
+    pages, vpp, vb = pipeline.vectors_to_pages(vectors)
+    cand = np.zeros((1, 8, 2), np.uint32)
+    cand[0, :, 0] = np.arange(8, dtype=np.float32).view(np.uint32)   # PQ distances only order the ranks
+    cand[0, :, 1] = np.arange(8)
+    q = np.zeros((1, d), np.float32)
+    kw = dict(top_n=8, top_k=1, tile=2, vectors_per_page=vpp, page_bytes=4096, vector_bytes=vb)
+    dists, ids, n_exact, _ = orc.rerank(cand, q, pages, np.float32, **kw)
+    assert n_exact == 8 and ids[0, 0] == 6 and dists[0, 0] == 1.0
+    dists, ids, n_exact, _ = orc.rerank(cand, q, pages, np.float32, early_stop_min_prefix=2, early_stop_patience_tiles=1, **kw)
+    # tile 1 (ranks 0-1): k-th 9, improved from inf -> stable 0; tile 2: 4 < 9 -> 0; tile 3: 4 == 4 -> stable 1 -> stop
+    assert n_exact == 6 and ids[0, 0] == 2 and dists[0, 0] == 4.0
+    assert ids[0, 6] == 0xFFFFFFFF and np.isinf(dists[0, 6])
+    dists, ids, n_exact, _ = orc.rerank(cand, q, pages, np.float32, early_stop_min_prefix=2, early_stop_patience_tiles=2, **kw)
+    assert n_exact == 8 and ids[0, 0] == 6   # tile 4 improves the best again before two stable tiles are seen

@@ -62,7 +62,9 @@ class BeamParams(C.Structure):
 
 class RerankParams(C.Structure):
     _fields_ = [("top_n", C.c_uint32), ("top_k", C.c_uint32), ("tile", C.c_uint32),
-                ("use_bound_filter", C.c_uint32)]
+                ("use_bound_filter", C.c_uint32), ("use_early_stop", C.c_uint32),
+                ("early_stop_min_prefix", C.c_uint32), ("early_stop_patience_tiles", C.c_uint32),
+                ("reserved", C.c_uint32)]
 
 
 class RvqModelView(C.Structure):

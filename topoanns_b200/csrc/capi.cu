@@ -297,6 +297,12 @@ TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams*
         if (error_bounds == nullptr)
             return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires residual PQ2 error bounds.");
     }
+    if (params->use_early_stop) {
+        if (params->top_k == 0 || params->top_k > 128)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires 1 <= top_k <= 128.");
+        if (params->early_stop_patience_tiles == 0)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires early_stop_patience_tiles >= 1.");
+    }
     TannStatus st = CheckShards(index->vectors, index->num_nodes, "vectors");
     if (st != TANN_OK) return st;
     TANN_CUDA(tann::LaunchRerank(*index, *params, candidates, capacity, num_queries, queries, query_kind,
@@ -564,6 +570,8 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         TANN_CUDA(tann::LaunchF32ToU8Checked(static_cast<const float*>(queries_dev), Q * d, s->d_queries_u8,
                                              s->d_not_u8, stream));
         if (rerank->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
+        if (rerank->use_early_stop && (rerank->top_k == 0 || rerank->top_k > 128 || rerank->early_stop_patience_tiles == 0))
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires 1 <= top_k <= 128 and patience >= 1.");
         TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
                                      s->d_ids, nullptr, stream, s->d_queries_u8, s->d_not_u8,
                                      /*only the first top_k ranks are packed below*/ rerank->top_k <= 32 ? rerank->top_k : 0));

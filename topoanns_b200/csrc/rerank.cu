@@ -206,8 +206,10 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(rr_smem);   // [padded]
     uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
     uint8_t* qrow = rr_smem + (((size_t)padded * 12 + 15) & ~(size_t)15);          // query row copy, 16-byte aligned
-    __shared__ float s_threshold, s_qnorm;
-    __shared__ unsigned int s_exact, s_filtered;
+    __shared__ float s_threshold, s_qnorm, s_prev_kth;
+    __shared__ unsigned int s_exact, s_filtered, s_stable, s_stop;
+    __shared__ float s_best[128];   // the top_k <= 128 smallest exact distances so far (bound filter, early stop)
+    const bool track_kth = p.use_bound_filter || p.use_early_stop;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t dim = ix.dim;
     // Float queries whose values are all integers in [0, 255] (checked on the device by the caller,
@@ -239,8 +241,10 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
         for (uint32_t i = tid; i < padded; i += kRerankThreads) keys[i] = kInvalidKey64;
         if (tid == 0) {
             s_threshold = __int_as_float(0x7f800000);
-            s_exact = 0; s_filtered = 0;
+            s_prev_kth = __int_as_float(0x7f800000);
+            s_exact = 0; s_filtered = 0; s_stable = 0; s_stop = 0;
         }
+        if (track_kth) s_best[tid] = __int_as_float(0x7f800000);   // 128 threads, 128 slots
         __syncthreads();
         if (p.use_bound_filter && tid == 0) {
             double s = 0.0;
@@ -351,22 +355,30 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                 }
             }
             __syncthreads();
-            if (p.use_bound_filter) {
-                if (tid == 0) {  // :541-571, k-th smallest over ranks [0, rb + rc)
-                    float best[128];
+            if (track_kth) {
+                if (tid == 0) {
+                    // k-th smallest exact distance over ranks [0, rb + rc) (:541-571): the sorted best-k
+                    // list is kept across tiles, only this tile's distances are inserted
                     const uint32_t k = p.top_k;
-                    for (uint32_t i = 0; i < k; ++i) best[i] = __int_as_float(0x7f800000);
-                    const uint32_t prefix = min(p.top_n, rb + rc);
-                    for (uint32_t r = 0; r < prefix; ++r) {
+                    for (uint32_t r = rb; r < rb + rc; ++r) {
                         const float x = FromOrderedBits((uint32_t)(keys[r] >> 32));
-                        if (!(x < best[k - 1])) continue;
+                        if (!(x < s_best[k - 1])) continue;
                         uint32_t ins = k - 1;
-                        while (ins > 0 && x < best[ins - 1]) { best[ins] = best[ins - 1]; --ins; }
-                        best[ins] = x;
+                        while (ins > 0 && x < s_best[ins - 1]) { s_best[ins] = s_best[ins - 1]; --ins; }
+                        s_best[ins] = x;
                     }
-                    s_threshold = best[k - 1];
+                    const float kth = s_best[k - 1];
+                    s_threshold = kth;
+                    if (p.use_early_stop) {   // src/io/bam_vector_provider.cu:1124-1135
+                        if (rb + rc >= p.early_stop_min_prefix && isfinite(kth)) {
+                            if (kth < s_prev_kth) s_stable = 0; else ++s_stable;
+                            if (s_stable >= p.early_stop_patience_tiles) s_stop = 1;
+                        }
+                        s_prev_kth = kth;
+                    }
                 }
                 __syncthreads();
+                if (s_stop) break;
             }
         }
         // final sort and output: bitonic network; the stages inside runs of 32 keys are done by one

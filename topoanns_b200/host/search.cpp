@@ -385,7 +385,7 @@ RerankBatchResult RerankFromHostResults(const SearchResources& resources, const 
     auto t0 = Clock::now();
     const CudaBuffer<QueryT> d_queries = CudaBuffer<QueryT>::CopyFromHost(queries);
     const double upload_ms = MsSince(t0);
-    TannRerankParams rp{top_n, static_cast<std::uint32_t>(params.top_k), 0, 0};
+    TannRerankParams rp{top_n, static_cast<std::uint32_t>(params.top_k), 0, 0, 0, 0, 0, 0};
     const DeviceRerank rr = RunRerankKernel(resources, view, rp, d_cand.get(), top_n, num_queries, d_queries.get(),
                                             KindOf<QueryT>(), nullptr, ctx);
     t0 = Clock::now();
@@ -439,8 +439,14 @@ RerankBatchResult RerankFromDeviceTraversal(const SearchResources& resources, co
         if (params.mode == RerankExecutionMode::kLinear) throw std::runtime_error(BuildErrorMessage(ctx, "PQ2 bound filter requires a non-linear GPU rerank path."));
         if (!resources.has_pq2_error_bounds()) throw std::runtime_error(BuildErrorMessage(ctx, "PQ2 bound filter requires residual PQ2 error bounds."));
     }
-    if (params.use_learned_stop || params.use_early_stop)
-        throw std::runtime_error(BuildErrorMessage(ctx, "early / learned rerank stops belong to the NVMe-backed persistent path and are not available."));
+    if (params.use_learned_stop)
+        throw std::runtime_error(BuildErrorMessage(ctx, "the learned rerank stop belongs to the NVMe-backed persistent path and is not available."));
+    if (params.use_early_stop) {
+        if (params.mode != RerankExecutionMode::kPersistent && params.mode != RerankExecutionMode::kTiled)
+            throw std::runtime_error(BuildErrorMessage(ctx, "rerank early stop requires the persistent or tiled mode."));
+        if (params.top_k == 0 || params.top_k > 128) throw std::runtime_error(BuildErrorMessage(ctx, "rerank early stop requires 1 <= top_k <= 128."));
+        if (params.early_stop_patience_tiles == 0) throw std::runtime_error(BuildErrorMessage(ctx, "rerank early stop requires early_stop_patience_tiles >= 1."));
+    }
     if (params.top_k > params.top_n) throw std::runtime_error(BuildErrorMessage(ctx, "top_k must not exceed top_n."));
 
     RerankBatchResult result;
@@ -493,7 +499,9 @@ RerankBatchResult RerankFromDeviceTraversal(const SearchResources& resources, co
     }
     const TannIndexView view = resources.MakeIndexView(true);
     TannRerankParams rp{static_cast<std::uint32_t>(params.top_n), static_cast<std::uint32_t>(params.top_k), tile,
-                        params.use_pq2_bound_filter ? 1u : 0u};
+                        params.use_pq2_bound_filter ? 1u : 0u, params.use_early_stop ? 1u : 0u,
+                        static_cast<std::uint32_t>(params.early_stop_min_prefix),
+                        static_cast<std::uint32_t>(params.early_stop_patience_tiles), 0u};
     const DeviceRerank rr = RunRerankKernel(resources, view, rp, cand, capacity, num_queries, d_queries.get(),
                                             TANN_KIND_FLOAT32,
                                             params.use_pq2_bound_filter ? resources.pq2_error_bounds_fp32().get() : nullptr, ctx);

@@ -39,12 +39,37 @@ def main() -> None:
     ap.add_argument("--entries", type=int, default=128)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--staged-table", action="store_true", help="build the query tables with tann_lut_build first")
+    ap.add_argument("--topology", default="hbm", choices=["hbm", "pinned-host"],
+                    help="where the adjacency lists live (pinned-host = mapped host memory read over PCIe)")
+    ap.add_argument("--cached-fraction", type=float, default=0.0,
+                    help="with --topology pinned-host: fraction of the rows (an id prefix) cached in HBM")
     a = ap.parse_args()
     cfg = dataclasses.replace(synth.CONFIGS[a.config], num_nodes=a.nodes, components=max(1, a.nodes // 1000),
                               num_queries=a.queries, kmeans_iters=5)
     s = synth.build(cfg, "cuda")
     ix = search.device_index_from_synth(s)
     q = s.queries.cuda().contiguous()
+    host_alloc = None
+    if a.topology == "pinned-host":
+        import ctypes as C
+
+        from . import capi
+        lib = capi.load()
+        nbytes = ix.adjacency.numel() * 4
+        hp, dp = C.c_void_p(), C.c_void_p()
+        capi.check(lib.tann_host_alloc_mapped(nbytes, C.byref(hp), C.byref(dp)))
+        host_alloc = hp
+        adj_host = ix.adjacency.cpu().numpy()   # keep the array alive across the copy
+        C.memmove(hp.value, adj_host.ctypes.data, nbytes)
+        del adj_host
+        cached = int(ix.num_nodes * a.cached_fraction)
+        ix = search.DeviceIndex(
+            num_nodes=ix.num_nodes, degree=ix.degree, dim=ix.dim, vector_kind=ix.vector_kind, codes=ix.codes,
+            vector_pages=ix.vector_pages, pq_tables_col_major=ix.pq_tables_col_major, pq_centroid=ix.pq_centroid,
+            pq_chunk_offsets=ix.pq_chunk_offsets, vector_bytes=ix.vector_bytes, vectors_per_page=ix.vectors_per_page,
+            adjacency_bases=[dp.value], adjacency_cache=ix.adjacency[:cached].clone() if cached else None,
+            adjacency_cached_rows=cached)
+        print(f"topology: {nbytes / 1e9:.2f} GB in mapped pinned host memory, {cached} rows ({a.cached_fraction:.0%}) cached in HBM")
     if cfg.rvq:
         model = search.rvq_model_from_synth(s)
         (offs, ids, _), ms = _time(lambda: model.device_entry_batch(q, a.entries), a.reps)
@@ -73,6 +98,9 @@ def main() -> None:
         _, ms = _time(lambda: search.rerank_exact(ix, rp, cand, q8), a.reps)
         gb = a.queries * a.top_n * s.vectors.shape[1] / 1e9
         print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}  (uint8 queries, integer path) {gb / ms * 1e3:.1f} GB/s")
+    if host_alloc is not None:
+        torch.cuda.synchronize()
+        capi.check(lib.tann_host_free(host_alloc))
 
 
 if __name__ == "__main__":

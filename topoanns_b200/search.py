@@ -73,9 +73,13 @@ class RerankExactParams:
     use_pq2_refine: bool = False
     use_pq2_bound_filter: bool = False
     pq2_refine_top_l: int = 0
+    use_early_stop: bool = False
+    early_stop_min_prefix: int = 32
+    early_stop_patience_tiles: int = 1
 
     def to_c(self) -> capi.RerankParams:
-        return capi.RerankParams(self.top_n, self.top_k, self.rank_tile_size, int(self.use_pq2_bound_filter))
+        return capi.RerankParams(self.top_n, self.top_k, self.rank_tile_size, int(self.use_pq2_bound_filter),
+                                 int(self.use_early_stop), self.early_stop_min_prefix, self.early_stop_patience_tiles, 0)
 
 
 @dataclass
