@@ -98,6 +98,22 @@ def main() -> None:
         _, ms = _time(lambda: search.rerank_exact(ix, rp, cand, q8), a.reps)
         gb = a.queries * a.top_n * s.vectors.shape[1] / 1e9
         print(f"rerank_exact {ms:.3f} ms  top_n={a.top_n}  (uint8 queries, integer path) {gb / ms * 1e3:.1f} GB/s")
+    if getattr(s, "pq2_tables", None) is not None:
+        # residual pq2 refine + bound filter (float configurations): second table build, refine, tiled rerank
+        t2 = s.pq2_tables.cuda().contiguous()
+        c2 = s.pq2_centroid.cuda().contiguous()
+        codes2 = s.pq2_codes.cuda().contiguous()
+        cross = search.pq2_cross_terms(ix.pq_chunk_offsets, s.pq_tables.cuda().contiguous(), ix.pq_centroid, t2, c2)
+        t2_cm = t2.t().contiguous()
+        lut2, ms = _time(lambda: search.lut_build(ix, q, tables_col_major=t2_cm, centroid=c2), a.reps)
+        print(f"lut_build (pq2) {ms:.3f} ms  {lut2.numel() * 4 / 1e6:.0f} MB written")
+        lr = min(a.top_l, cap)
+        refined, ms = _time(lambda: search.pq2_refine(cand, stats, lr, codes2, lut2, base_codes=ix.codes, cross_terms=cross), a.reps)
+        print(f"pq2_refine {ms:.3f} ms  refine_top_l={lr}")
+        eps = s.pq2_error_bounds.cuda().contiguous()
+        rp2 = search.RerankExactParams(top_k=10, top_n=min(a.top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
+        (_, _, n_exact, n_flt), ms = _time(lambda: search.rerank_exact(ix, rp2, refined, q, eps), a.reps)
+        print(f"rerank_exact (tiled, bound filter) {ms:.3f} ms  exact={n_exact} filtered={n_flt}")
     if host_alloc is not None:
         torch.cuda.synchronize()
         capi.check(lib.tann_host_free(host_alloc))
