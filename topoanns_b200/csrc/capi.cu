@@ -485,10 +485,7 @@ TannStatus tann_searcher_set_rvq(TannSearcher* s, const TannRvqModelView* rvq) {
 TannStatus tann_searcher_set_pq2(TannSearcher* s, const TannPq2View* pq2) {
     if (!s) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_pq2: null searcher.");
     if (!pq2 || !pq2->enabled) { s->has_pq2 = false; return TANN_OK; }
-    if (s->d_lut2 == nullptr) {
-        TANN_CUDA(cudaMalloc((void**)&s->d_lut2, s->max_queries * (size_t)s->ix.num_chunks * 256 * 4));
-    }
-    s->pq2 = *pq2;
+    s->pq2 = *pq2;   // no second-level table buffer: the refine kernel computes the entries it reads
     s->has_pq2 = true;
     return TANN_OK;
 }
@@ -554,13 +551,15 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         const TannPq2View& p2 = s->pq2;
         // src/search/rerank_exact.cu:2610-2615
         const uint32_t lr = p2.refine_top_l == 0 ? capacity : (p2.refine_top_l < capacity ? p2.refine_top_l : capacity);
-        st = tann_lut_build(p2.tables_col_major, p2.centroid, p2.chunk_offsets, d, s->ix.num_chunks, qf32,
-                            TANN_KIND_FLOAT32, Q, s->d_lut2, stream);
-        if (st != TANN_OK) return st;
-        st = tann_pq2_refine(s->d_cand, s->d_stats, Q, capacity, lr, p2.residual ? &s->ix.codes : nullptr,
-                             &p2.codes, s->ix.num_chunks, s->d_lut2, p2.cross_terms, s->d_cand_refined,
-                             nullptr, stream);
-        if (st != TANN_OK) return st;
+        // Same checks as tann_pq2_refine (src/search/rerank_exact.cu:2285-2296); the second-level table
+        // entries are computed inside the refine kernel, so no Q x M x 256 table is built here.
+        if (s->ix.num_chunks > 256) return Fail(TANN_ERR_UNSUPPORTED, "tann_pq2_refine: PQ2 num_chunks exceeds kernel specialization limit.");
+        if (lr > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_pq2_refine: refine_top_l exceeds device bitonic sort limit.");
+        if (p2.residual && p2.cross_terms == nullptr)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_pq2_refine: residual refine needs cross terms.");
+        TANN_CUDA(tann::LaunchPq2Refine(s->d_cand, s->d_stats, Q, capacity, lr, p2.residual ? &s->ix.codes : nullptr,
+                                        p2.codes, s->ix.num_chunks, /*lut2=*/nullptr, p2.cross_terms, s->d_cand_refined,
+                                        stream, p2.tables_col_major, p2.centroid, p2.chunk_offsets, qf32, d));
         cand = s->d_cand_refined;
         capacity = lr;
         err = p2.error_bounds;

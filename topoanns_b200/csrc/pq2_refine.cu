@@ -3,6 +3,12 @@
 // plain, :773-879 residual): lane l sums chunks l, l+32, ... then the shuffle tree; the residual
 // form adds (LUT2 + cross term) per chunk and the base distance once at the end. One block per
 // query (persistent), one warp per rank, 64-bit keys sorted in shared memory.
+//
+// The second-level table entries can come from a table built beforehand (tann_lut_build, what the
+// reference does) or be computed where they are needed: a refine reads refine_top_l x M of the M x 256
+// entries of a query, so summing the chunk's dims on the spot - the same ascending-dim FMA chain as
+// the table build (src/search/pq_query_tables.cu:33-52), hence the same bits - saves writing and
+// reading Q x M x 1 KB of tables.
 #include "tann_common.cuh"
 #include "tann_launch.h"
 
@@ -29,13 +35,20 @@ __global__ void __launch_bounds__(kPq2Threads)
 pq2_refine_kernel(const Cand* __restrict__ cand, const uint32_t* __restrict__ stats, uint64_t Q,
                   uint32_t capacity, uint32_t Lr, uint32_t padded, int has_base, TannShards base_codes,
                   TannShards pq2_codes, uint32_t M, const float* __restrict__ lut2,
-                  const float* __restrict__ cross, Cand* __restrict__ out) {
+                  const float* __restrict__ cross, Cand* __restrict__ out,
+                  const float* __restrict__ t2_col_major, const float* __restrict__ mu2,
+                  const uint32_t* __restrict__ chunk_offsets, const float* __restrict__ queries_f32, uint32_t dim) {
     extern __shared__ unsigned long long pq2_keys[];
+    float* sq = reinterpret_cast<float*>(pq2_keys + padded);   // [dim] query minus centroid (table-free form)
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     constexpr unsigned long long kInvalidKey = 0xff800000ffffffffull;
     for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
         const uint32_t valid = min(stats[q * 8 + 4], Lr);
-        const float* lut = lut2 + q * (uint64_t)M * kCentroids;
+        const float* lut = lut2 != nullptr ? lut2 + q * (uint64_t)M * kCentroids : nullptr;
+        if (lut == nullptr) {
+            for (uint32_t i = threadIdx.x; i < dim; i += kPq2Threads) sq[i] = queries_f32[q * dim + i] - __ldg(mu2 + i);
+            __syncthreads();
+        }
         for (uint32_t rank = warp; rank < padded; rank += kPq2Threads / 32) {
             unsigned long long key = kInvalidKey;
             if (rank < valid) {
@@ -47,12 +60,21 @@ pq2_refine_kernel(const Cand* __restrict__ cand, const uint32_t* __restrict__ st
                     float partial = 0.0f;
                     for (uint32_t m = lane; m < M; m += 32) {
                         const uint32_t rc = rc_row[m];
+                        float entry;
+                        if (lut != nullptr) {
+                            entry = lut[m * kCentroids + rc];
+                        } else {
+                            entry = 0.0f;
+                            for (uint32_t k = __ldg(chunk_offsets + m); k < __ldg(chunk_offsets + m + 1); ++k) {
+                                const float diff = __ldg(t2_col_major + (size_t)k * kCentroids + rc) - sq[k];
+                                entry = fmaf(diff, diff, entry);
+                            }
+                        }
                         if (has_base) {
                             const uint32_t bc = bc_row[m];
-                            partial += lut[m * kCentroids + rc] +
-                                       __ldg(cross + ((size_t)m * kCentroids + bc) * kCentroids + rc);
+                            partial += entry + __ldg(cross + ((size_t)m * kCentroids + bc) * kCentroids + rc);
                         } else {
-                            partial += lut[m * kCentroids + rc];
+                            partial += entry;
                         }
                     }
                     partial = WarpTreeSum(partial);
@@ -98,11 +120,13 @@ cross_terms_kernel(uint32_t dim, uint32_t M, const uint32_t* __restrict__ offs,
 cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q, uint32_t capacity,
                             uint32_t refine_top_l, const TannShards* base_codes,
                             const TannShards& pq2_codes, uint32_t M, const float* lut2,
-                            const float* cross_terms, void* out, cudaStream_t stream) {
+                            const float* cross_terms, void* out, cudaStream_t stream,
+                            const float* t2_col_major, const float* mu2, const uint32_t* chunk_offsets,
+                            const float* queries_f32, uint32_t dim) {
     if (Q == 0 || refine_top_l == 0) return cudaSuccess;
     uint32_t padded = 1;
     while (padded < refine_top_l) padded <<= 1;
-    const size_t smem = (size_t)padded * 8;
+    const size_t smem = (size_t)padded * 8 + (lut2 == nullptr ? (size_t)dim * 4 : 0);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(pq2_refine_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -113,7 +137,7 @@ cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q,
     pq2_refine_kernel<<<(unsigned)(Q < cap ? Q : cap), kPq2Threads, smem, stream>>>(
         static_cast<const Cand*>(cand), stats, Q, capacity, refine_top_l, padded,
         base_codes != nullptr ? 1 : 0, base_codes != nullptr ? *base_codes : none, pq2_codes, M, lut2,
-        cross_terms, static_cast<Cand*>(out));
+        cross_terms, static_cast<Cand*>(out), t2_col_major, mu2, chunk_offsets, queries_f32, dim);
     return cudaGetLastError();
 }
 

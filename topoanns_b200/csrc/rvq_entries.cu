@@ -450,7 +450,7 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
                     }
                     const float* col = cb + c0;
                     const float* xq = x + qg * 8;
-#pragma unroll 2
+#pragma unroll 4
                     for (uint32_t k = 0; k < dim; ++k) {
                         const float4 w = *reinterpret_cast<const float4*>(col + (size_t)k * count);
                         const float4 xa = *reinterpret_cast<const float4*>(xq + k * XS);

@@ -34,7 +34,11 @@ cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, con
 cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q, uint32_t capacity,
                             uint32_t refine_top_l, const TannShards* base_codes,
                             const TannShards& pq2_codes, uint32_t M, const float* lut2,
-                            const float* cross_terms, void* out, cudaStream_t stream);
+                            const float* cross_terms, void* out, cudaStream_t stream,
+                            /* with lut2 == nullptr the table entries are computed from these instead */
+                            const float* t2_col_major = nullptr, const float* mu2 = nullptr,
+                            const uint32_t* chunk_offsets = nullptr, const float* queries_f32 = nullptr,
+                            uint32_t dim = 0);
 cudaError_t LaunchCrossTerms(uint32_t dim, uint32_t M, const uint32_t* chunk_offsets, const float* t1,
                              const float* mu1, const float* t2, const float* mu2, float* out,
                              cudaStream_t stream);

@@ -114,6 +114,14 @@ def main() -> None:
         rp2 = search.RerankExactParams(top_k=10, top_n=min(a.top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
         (_, _, n_exact, n_flt), ms = _time(lambda: search.rerank_exact(ix, rp2, refined, q, eps), a.reps)
         print(f"rerank_exact (tiled, bound filter) {ms:.3f} ms  exact={n_exact} filtered={n_flt}")
+        if cfg.rvq:
+            sr = search.Searcher(ix, a.queries, cap, min(a.top_n, lr), a.entries)
+            sr.set_rvq(model, a.entries)
+            sr.set_pq2(search.Pq2Resources(codes=codes2, tables_col_major=t2_cm, centroid=c2, chunk_offsets=ix.pq_chunk_offsets,
+                                           cross_terms=cross, error_bounds=eps), lr)
+            _, ms = _time(lambda: sr.run_device(q, p, rp2), a.reps)
+            print(f"searcher whole path (rvq, beam, table-free pq2 refine, bound-filtered rerank, top-k) {ms:.3f} ms")
+            sr.close()
     if host_alloc is not None:
         torch.cuda.synchronize()
         capi.check(lib.tann_host_free(host_alloc))
