@@ -214,6 +214,27 @@ void TestRerankAndEndToEnd() {
     CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, badp));
     badp = params; badp.rerank.use_learned_stop = true;
     CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, badp));
+    // rerank early stop (stable-tile rule): with tiles of one rank, min_prefix 1 and patience 1 the rerank of
+    // query 0 ends at the first tile that does not improve the best distance, so fewer than the 10 exact
+    // distances of the full run are computed; a rule that can never fire changes nothing; linear mode rejects it
+    {
+        TopoAnnsSearchParams ep = params;
+        ep.rerank.top_k = 1;
+        ep.rerank.mode = RerankExecutionMode::kPersistent;
+        ep.rerank.rank_tile_size = 1;
+        ep.rerank.use_early_stop = true;
+        ep.rerank.early_stop_min_prefix = 1;
+        ep.rerank.early_stop_patience_tiles = 1;
+        const auto early = TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, ep);
+        CHECK_TRUE(early.rerank_stats.exact_distance_count < std::size_t{10});
+        CHECK_TRUE(early.rerank_stats.exact_distance_count >= std::size_t{4});   // at least two tiles per query
+        ep.rerank.early_stop_min_prefix = 1000;
+        const auto never = TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, ep);
+        CHECK_EQ(never.rerank_stats.exact_distance_count, std::size_t{10});
+        CHECK_EQ(never.queries[0].rerank.topk[0].node_id, base.queries[0].rerank.topk[0].node_id);
+        ep.rerank.mode = RerankExecutionMode::kLinear;
+        CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, ep));
+    }
     // the pinned-host page provider gives the same fused result
     r.AttachVectorPageProvider(std::make_shared<PinnedHostVectorPageProvider>(fx::Tmp("e2e_vectors.ssd")));
     const auto hosted = TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, params);
