@@ -48,7 +48,10 @@ def _load(tmp, tag, name, dtype):
 
 
 def _report(name, payload):
-    out = os.path.join(ROOT, "gpurun_out")
+    """Appends one JSON record per case to $TANN_REPORT_DIR/reference_pin.jsonl when that variable is set."""
+    out = os.environ.get("TANN_REPORT_DIR")
+    if not out:
+        return
     os.makedirs(out, exist_ok=True)
     with open(os.path.join(out, "reference_pin.jsonl"), "a") as f:
         f.write(json.dumps({"case": name, **payload}) + "\n")
