@@ -278,20 +278,13 @@ TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks, const uint32_
     return TANN_OK;
 }
 
-TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams* params,
-                             const void* candidates, uint32_t capacity, uint64_t num_queries,
-                             const void* queries, uint32_t query_kind, const float* error_bounds,
-                             float* out_dists, uint32_t* out_ids, unsigned long long* out_counts,
-                             uint32_t* status, tann_stream_t stream) {
-    (void)status;
-    if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null index or params.");
-    if (num_queries == 0 || params->top_n == 0) return TANN_OK;
+// Parameter rules of the rerank (src/search/rerank_exact.cu:2181-2190, :2564-2585), shared by
+// tann_rerank_exact and the searcher.
+static TannStatus CheckRerank(const TannIndexView* index, const TannRerankParams* params, const float* error_bounds) {
     if (index->vectors.base[0] == nullptr || index->vector_bytes == 0 || index->vectors_per_page == 0)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: Vector store must be loaded before rerank.");
-    if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
-        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null pointer.");
     if (params->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
-    if (params->use_bound_filter) {  // src/search/rerank_exact.cu:2564-2585
+    if (params->use_bound_filter) {
         if (params->top_k == 0 || params->top_k > 128)
             return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires 1 <= top_k <= 128.");
         if (error_bounds == nullptr)
@@ -303,7 +296,20 @@ TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams*
         if (params->early_stop_patience_tiles == 0)
             return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires early_stop_patience_tiles >= 1.");
     }
-    TannStatus st = CheckShards(index->vectors, index->num_nodes, "vectors");
+    return CheckShards(index->vectors, index->num_nodes, "vectors");
+}
+
+TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams* params,
+                             const void* candidates, uint32_t capacity, uint64_t num_queries,
+                             const void* queries, uint32_t query_kind, const float* error_bounds,
+                             float* out_dists, uint32_t* out_ids, unsigned long long* out_counts,
+                             uint32_t* status, tann_stream_t stream) {
+    (void)status;
+    if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null index or params.");
+    if (num_queries == 0 || params->top_n == 0) return TANN_OK;
+    if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null pointer.");
+    TannStatus st = CheckRerank(index, params, error_bounds);
     if (st != TANN_OK) return st;
     TANN_CUDA(tann::LaunchRerank(*index, *params, candidates, capacity, num_queries, queries, query_kind,
                                  error_bounds, out_dists, out_ids, out_counts, (cudaStream_t)stream));
@@ -564,20 +570,17 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         capacity = lr;
         err = p2.error_bounds;
     }
-    if (query_kind == TANN_KIND_FLOAT32 && s->ix.vector_kind == TANN_KIND_UINT8 && !rerank->use_bound_filter) {
-        // integer-valued float queries (the usual case for uint8 data) can use the integer distance path
-        TANN_CUDA(tann::LaunchF32ToU8Checked(static_cast<const float*>(queries_dev), Q * d, s->d_queries_u8,
-                                             s->d_not_u8, stream));
-        if (rerank->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
-        if (rerank->use_early_stop && (rerank->top_k == 0 || rerank->top_k > 128 || rerank->early_stop_patience_tiles == 0))
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires 1 <= top_k <= 128 and patience >= 1.");
-        TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
-                                     s->d_ids, nullptr, stream, s->d_queries_u8, s->d_not_u8,
-                                     /*only the first top_k ranks are packed below*/ rerank->top_k <= 32 ? rerank->top_k : 0));
-    } else {
-        st = tann_rerank_exact(&s->ix, rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
-                               s->d_ids, nullptr, nullptr, stream);
+    if (rerank->top_n != 0) {
+        st = CheckRerank(&s->ix, rerank, err);
         if (st != TANN_OK) return st;
+        const bool u8_copy = query_kind == TANN_KIND_FLOAT32 && s->ix.vector_kind == TANN_KIND_UINT8 && !rerank->use_bound_filter;
+        if (u8_copy)   // integer-valued float queries (the usual case for uint8 data) can use the integer distance path
+            TANN_CUDA(tann::LaunchF32ToU8Checked(static_cast<const float*>(queries_dev), Q * d, s->d_queries_u8,
+                                                 s->d_not_u8, stream));
+        // only the first top_k ranks are packed below: a top-k tournament replaces the full sort when k <= 32
+        TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
+                                     s->d_ids, nullptr, stream, u8_copy ? s->d_queries_u8 : nullptr,
+                                     u8_copy ? s->d_not_u8 : nullptr, rerank->top_k <= 32 ? rerank->top_k : 0));
     }
     st = tann_topk_pack(s->d_dists, s->d_ids, Q, rerank->top_n, rerank->top_k, s->d_topk_dists,
                         s->d_topk_ids, stream);
