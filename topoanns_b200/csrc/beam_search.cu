@@ -360,6 +360,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
     const uint32_t lane = tid & 31;
     const uint32_t my_k = deg ? tid / deg : 0u, my_j = tid - my_k * deg;  // slot of this thread (kSingle)
 
+    __shared__ __align__(8) unsigned long long lut_barrier;   // completion of the bulk copy of a caller's table
+    uint32_t lut_phase = 0;
+    bool lut_bulk_ok = true;
+    if (a.lut != nullptr) {
+        if (tid == 0) BarrierInit(&lut_barrier, 1);
+        __syncthreads();
+    }
     // Chunks of equal width (the usual case) take the unrolled table build.
     uint32_t uniform_sub = 0;
     if (a.lut == nullptr) {
@@ -376,11 +383,20 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         long long prof_t = clock64();
 #endif
         // ---- per-query set-up --------------------------------------------------------------
+        bool lut_copy_pending = false;
         if (a.lut != nullptr) {
-            const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
-            float4* dst = reinterpret_cast<float4*>(lut);
+            // A table given by the caller is staged with one bulk asynchronous copy (rows of 1 KB, 16-byte
+            // aligned) while the block clears its lists; a table at an odd address takes ordinary loads.
+            const float* src_lut = a.lut + q * (uint64_t)M * kCentroids;
+            if (lut_bulk_ok && (reinterpret_cast<uintptr_t>(src_lut) & 15u) == 0) {
+                if (tid == 0) BulkLoadToShared(lut, src_lut, M * kCentroids * 4, &lut_barrier);
+                lut_copy_pending = true;
+            } else {
+                const float4* src = reinterpret_cast<const float4*>(src_lut);
+                float4* dst = reinterpret_cast<float4*>(lut);
 #pragma unroll 8
-            for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
+                for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
+            }
         } else {
             // src/search/pq_query_tables.cu:33-52
             for (uint32_t i = tid; i < d; i += kBeamThreads)
@@ -410,6 +426,16 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             s_surv = 0; s_pass = 0;
         }
         if (tid < 32) ctl.ls_prev_ids[tid] = kInvalid;
+        if (lut_copy_pending) {
+            const bool arrived = BarrierWaitBounded(&lut_barrier, lut_phase & 1u);
+            ++lut_phase;
+            if (!__syncthreads_and(arrived)) {   // never seen; the bounded poll keeps the block from waiting forever
+                lut_bulk_ok = false;
+                const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
+                float4* dst = reinterpret_cast<float4*>(lut);
+                for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
+            }
+        }
         __syncthreads();
 
         TANN_PHASE(0);  // 0: set-up (table build, clears)

@@ -379,6 +379,7 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
     __shared__ ArgMin scratch[kWarps][8];
     __shared__ int best_coarse[kSmemMaxPerBlock];
     __shared__ int best_cluster[kSmemMaxPerBlock];
+    __shared__ __align__(8) unsigned long long copy_barrier;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t cg = tid & 63, qg = tid >> 6;
 
@@ -387,15 +388,24 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
     const uint64_t q_begin = (uint64_t)blockIdx.x * per_block;
     if (q_begin >= Q) return;
     const uint32_t n_mine = (uint32_t)min((uint64_t)per_block, Q - q_begin);
+    if (tid == 0) BarrierInit(&copy_barrier, 1);
+    bool bulk_ok = true;   // block-uniform: cleared if a bulk copy did not complete in time
 
     for (int level = 0; level < 2; ++level) {
         const float* book_t = level == 0 ? coarse_t : fine_t;
         const float* book_norms = level == 0 ? coarse_norms : fine_norms;
         const uint32_t count = level == 0 ? nc : nf;
-        __syncthreads();   // the previous level's readers are done with cb
+        __syncthreads();   // the previous level's readers are done with cb (and the barrier is initialised)
+        const uint32_t book_bytes = count * dim * 4;
+        const bool bulk = bulk_ok;
+        if (bulk) {
+            // one bulk copy stages the level's codebook while the block fills and norms its first tile
+            if (tid == 0) BulkLoadToShared(cb, book_t, book_bytes, &copy_barrier);
+        } else {
 #pragma unroll 8
-        for (uint32_t i = tid; i < count * dim / 4; i += kSmemThreads)
-            reinterpret_cast<float4*>(cb)[i] = __ldg(reinterpret_cast<const float4*>(book_t) + i);
+            for (uint32_t i = tid; i < book_bytes / 16; i += kSmemThreads)
+                reinterpret_cast<float4*>(cb)[i] = __ldg(reinterpret_cast<const float4*>(book_t) + i);
+        }
         for (uint32_t t0 = 0; t0 < n_mine; t0 += QB) {
             const int nq = (int)min((uint32_t)QB, n_mine - t0);
             __syncthreads();   // cb is loaded; the previous tile's readers are done with x
@@ -431,6 +441,16 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
                 }
             }
             __syncthreads();
+            if (bulk && t0 == 0) {
+                const bool arrived = BarrierWaitBounded(&copy_barrier, (uint32_t)level & 1u);
+                if (!__syncthreads_and(arrived)) {   // never seen; the bounded poll keeps the block from waiting forever
+                    bulk_ok = false;
+#pragma unroll 8
+                    for (uint32_t i = tid; i < book_bytes / 16; i += kSmemThreads)
+                        reinterpret_cast<float4*>(cb)[i] = __ldg(reinterpret_cast<const float4*>(book_t) + i);
+                    __syncthreads();
+                }
+            }
             ArgMin best[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) { best[j].d = __int_as_float(0x7f800000); best[j].idx = 0x7fffffff; }

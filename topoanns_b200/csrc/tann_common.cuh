@@ -110,6 +110,38 @@ __device__ __forceinline__ unsigned long long WarpSortKey(unsigned long long k, 
     return k;
 }
 
+// ---- bulk asynchronous copy (TMA, untiled form) of a contiguous global range into shared memory ----
+// One thread arms an mbarrier with the byte count and issues the copies; every thread then polls the
+// barrier's phase. Source, destination and size are multiples of 16 bytes. The poll is bounded: if the
+// phase does not complete within the limit the caller loads the range with ordinary loads instead.
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void BarrierInit(unsigned long long* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(SmemAddr(bar)), "r"(arrivals) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void BulkLoadToShared(void* dst, const void* src, uint32_t bytes, unsigned long long* bar) {
+    constexpr uint32_t kChunk = 32768;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // earlier generic accesses to dst come first
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(SmemAddr(bar)), "r"(bytes) : "memory");
+    for (uint32_t off = 0; off < bytes; off += kChunk) {
+        const uint32_t n = min(kChunk, bytes - off);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(SmemAddr(static_cast<char*>(dst) + off)), "l"(static_cast<const char*>(src) + off), "r"(n),
+                       "r"(SmemAddr(bar))
+                     : "memory");
+    }
+}
+__device__ __forceinline__ bool BarrierWaitBounded(unsigned long long* bar, uint32_t parity) {
+    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(SmemAddr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+        __nanosleep(32);
+    }
+    return false;
+}
+
 template <typename T>
 __device__ __forceinline__ float LoadAsFloat(const void* p, uint32_t kind, uint64_t i) {
     if (kind == TANN_KIND_FLOAT32) return static_cast<const float*>(p)[i];
