@@ -356,6 +356,31 @@ def test_rerank_early_stop_matches_checker(min_prefix, patience):
     assert n2 == n_full and torch.equal(d2, d3) and torch.equal(i2, i3)
 
 
+def test_rerank_int8_vectors():
+    """Stored int8 vectors (the third scalar kind of the vector store) with int8 and float queries."""
+    s, host = small_index()
+    Q = s.queries.shape[0]
+    v8 = (s.vectors.to(torch.int16) - 128).to(torch.int8).cuda().contiguous()          # signed copy of the uint8 data
+    base = device_index(s)
+    ix = search.device_index_from_arrays(adjacency=host["adjacency"], codes=host["codes"], vectors=v8.cpu().numpy(),
+                                         pq_tables_row_major=host["pq_tables"], pq_centroid=host["pq_centroid"],
+                                         pq_chunk_offsets=host["pq_chunk_offsets"])
+    assert ix.vector_kind == capi.KIND_INT8
+    eo, ei = fixed_entries(Q, [s.medoid])
+    p = search.TopologySearchParams(top_l=64, search_width=2, max_expansions=4096)
+    cand, _ = search.beam_search(base, p, eo, ei, queries=s.queries.cuda().contiguous(), capacity=p.capacity(48))
+    pages, vpp, vb = pipeline.vectors_to_pages(v8.cpu().numpy())
+    rp = search.RerankExactParams(top_k=10, top_n=48)
+    q_i8 = (s.queries - 128).clamp(-128, 127).to(torch.int8).cuda().contiguous()
+    for qt in (q_i8, q_i8.float().contiguous()):
+        d, i, n_exact, _ = search.rerank_exact(ix, rp, cand, qt)
+        rd, ri, rn, _ = orc.rerank(np_u32(cand), qt.cpu().numpy(), pages, np.int8, top_n=48, top_k=10,
+                                   vectors_per_page=vpp, page_bytes=4096, vector_bytes=vb)
+        assert n_exact == rn
+        assert np.array_equal(np_u32(i), ri)
+        assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
+
+
 def host_pages(host):
     if host.get("pages") is None:
         pages, vpp, vb = pipeline.vectors_to_pages(host["vectors"])

@@ -355,6 +355,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
     __shared__ BeamCtl ctl;
     __shared__ uint32_t s_surv, s_pass;
+    __shared__ uint32_t s_half_rank[64];   // partial ranks of the split rank count (33..64 survivors)
     __shared__ uint32_t s_sel[kBeamThreads / 32][TANN_MAX_SEARCH_WIDTH];  // selected nodes, one copy per warp
     const uint32_t tid = threadIdx.x;
     const uint32_t lane = tid & 31;
@@ -696,7 +697,27 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 bool pred = false;
                 unsigned long long k = kInvalidKey;
                 uint32_t rank = 0;
-                if (n > 32) {
+                if (n > 32 && n <= 64) {
+                    // 33..64 survivors: the n x n comparisons are split over all 128 threads. Thread t
+                    // compares key t & 63 with one half of the keys (a warp reads the same key at a time,
+                    // i.e. broadcasts); the half counts meet in shared memory.
+                    const uint32_t i = tid & 63u, part = tid >> 6;
+                    const uint32_t half = (n + 1) / 2;
+                    const uint32_t jb = part * half, je = min(n, jb + half);
+                    uint32_t cnt = 0;
+                    if (i < n) {
+                        k = fkey[i];
+#pragma unroll 8
+                        for (uint32_t j = jb; j < je; ++j) {
+                            const unsigned long long kj = fkey[j];
+                            cnt += (kj < k || (kj == k && j < i)) ? 1u : 0u;
+                        }
+                        if (part == 1) s_half_rank[i] = cnt;
+                    }
+                    __syncthreads();
+                    if (part == 0 && i < n) rank = cnt + s_half_rank[i];
+                    else k = kInvalidKey;   // the upper half only helped counting
+                } else if (n > 64) {
                     // Long survivor lists (the list is not full yet): every warp sorts its 32 keys
                     // with shuffles, then a key's rank is its place in its own run plus its lower /
                     // upper bounds in the other runs (runs in front win ties, so ranks are distinct).
