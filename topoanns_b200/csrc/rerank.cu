@@ -193,7 +193,7 @@ __device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const 
     }
 }
 
-__global__ void __launch_bounds__(kRerankThreads)
+__global__ void __launch_bounds__(kRerankThreads, 8)
 rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, const Cand* __restrict__ cand,
               uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
               const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
@@ -280,13 +280,16 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                 }
                 keys[r] = slot;
             }
-            if (n_act) atomicAdd(&s_exact, n_act);
-            if (n_flt) atomicAdd(&s_filtered, n_flt);
+            n_act = __reduce_add_sync(kFull, n_act);   // one shared-memory atomic per warp, not per thread
+            n_flt = __reduce_add_sync(kFull, n_flt);
+            if (lane == 0 && n_act) atomicAdd(&s_exact, n_act);
+            if (lane == 0 && n_flt) atomicAdd(&s_filtered, n_flt);
             __syncthreads();
             // ---- distances --------------------------------------------------------------------
             const uint32_t end = rb + rc;
             if (octet_int) {
-                if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                if (rc >= 128) OctetRanksInt<8>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                else if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
                 else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
             } else if (octet_f32) {
                 if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
