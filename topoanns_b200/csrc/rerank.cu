@@ -193,7 +193,7 @@ __device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const 
     }
 }
 
-__global__ void __launch_bounds__(kRerankThreads, 8)
+__global__ void __launch_bounds__(kRerankThreads)
 rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, const Cand* __restrict__ cand,
               uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
               const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
@@ -288,8 +288,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
             // ---- distances --------------------------------------------------------------------
             const uint32_t end = rb + rc;
             if (octet_int) {
-                if (rc >= 128) OctetRanksInt<8>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-                else if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+                if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
                 else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
             } else if (octet_f32) {
                 if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
