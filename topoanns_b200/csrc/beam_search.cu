@@ -249,66 +249,6 @@ __device__ __forceinline__ float AdcTreeThread(const float* lut, const uint8_t* 
     return total;
 }
 
-// Query look-up table (src/search/pq_query_tables.cu:33-52), four consecutive centroids per thread
-// and step: one 16-byte load per dim and the same per-entry FMA chain (ascending dim) as the
-// one-entry form. kSub = dims per chunk when every chunk has that many: the loads of a step
-// (sixteen per thread) are then all issued before the first is used, which is what keeps the
-// 128 KB table stream from L2 from being latency-bound.
-template <int kSub>
-__device__ __forceinline__ void BuildLutUniform(float* lut, const float* sq, const float* tables,
-                                                uint32_t M, uint32_t tid) {
-    constexpr int kItems = kSub <= 2 ? 8 : (kSub <= 4 ? 4 : 2);   // 16 loads in flight per thread
-    const uint32_t total = M * (kCentroids / 4);
-    for (uint32_t item0 = tid; item0 < total; item0 += kBeamThreads * kItems) {
-        float4 t[kItems][kSub];
-#pragma unroll
-        for (int u = 0; u < kItems; ++u) {
-            const uint32_t item = item0 + u * kBeamThreads;
-            if (item < total) {
-                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
-#pragma unroll
-                for (int sd = 0; sd < kSub; ++sd)
-                    t[u][sd] = __ldg(reinterpret_cast<const float4*>(
-                        tables + (size_t)(m * kSub + sd) * kCentroids + c4));
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kItems; ++u) {
-            const uint32_t item = item0 + u * kBeamThreads;
-            if (item < total) {
-                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
-                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-#pragma unroll
-                for (int sd = 0; sd < kSub; ++sd) {
-                    const float sv = sq[m * kSub + sd];
-                    float df = t[u][sd].x - sv; acc.x = fmaf(df, df, acc.x);
-                    df = t[u][sd].y - sv; acc.y = fmaf(df, df, acc.y);
-                    df = t[u][sd].z - sv; acc.z = fmaf(df, df, acc.z);
-                    df = t[u][sd].w - sv; acc.w = fmaf(df, df, acc.w);
-                }
-                *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
-            }
-        }
-    }
-}
-
-__device__ __noinline__ void BuildLutGeneric(float* lut, const float* sq, const uint32_t* offs,
-                                             const float* tables, uint32_t M, uint32_t tid) {
-    for (uint32_t item = tid; item < M * (kCentroids / 4); item += kBeamThreads) {
-        const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
-        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
-            const float4 t = __ldg(reinterpret_cast<const float4*>(tables + (size_t)dim * kCentroids + c4));
-            const float sv = sq[dim];
-            float df = t.x - sv; acc.x = fmaf(df, df, acc.x);
-            df = t.y - sv; acc.y = fmaf(df, df, acc.y);
-            df = t.z - sv; acc.z = fmaf(df, df, acc.z);
-            df = t.w - sv; acc.w = fmaf(df, df, acc.w);
-        }
-        *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
-    }
-}
-
 // Bitonic sort of F keys held in shared memory (any power of two F).
 __device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
     for (uint32_t k = 2; k <= F; k <<= 1) {
@@ -405,13 +345,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             for (uint32_t i = tid; i <= M; i += kBeamThreads) offs[i] = __ldg(a.ix.pq_chunk_offsets + i);
             __syncthreads();
             switch (uniform_sub) {
-                case 1: BuildLutUniform<1>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                case 2: BuildLutUniform<2>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                case 3: BuildLutUniform<3>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                case 4: BuildLutUniform<4>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                case 6: BuildLutUniform<6>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                case 8: BuildLutUniform<8>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
-                default: BuildLutGeneric(lut, sq, offs, a.ix.pq_tables_col_major, M, tid); break;
+                case 1: BuildLutUniform<1, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 2: BuildLutUniform<2, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 3: BuildLutUniform<3, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 4: BuildLutUniform<4, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 6: BuildLutUniform<6, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                case 8: BuildLutUniform<8, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
+                default: BuildLutGeneric<kBeamThreads>(lut, sq, offs, a.ix.pq_tables_col_major, M, tid); break;
             }
         }
         // cand_b needs no clear: a merge writes all C elements of the buffer it fills.

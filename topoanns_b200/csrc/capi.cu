@@ -1,6 +1,7 @@
 // C ABI of the library: argument checks, launches, and the searcher that chains the whole path.
 #include <cuda_runtime.h>
 #include <stdarg.h>
+#include <stdint.h>
 #include <stdio.h>
 #include <string.h>
 
@@ -160,6 +161,8 @@ TannStatus tann_lut_build(const float* tables_col_major, const float* centroid,
     if (num_queries == 0) return TANN_OK;
     if (!tables_col_major || !centroid || !chunk_offsets || !queries || !out_tables)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_lut_build: null pointer.");
+    if (((reinterpret_cast<uintptr_t>(tables_col_major) | reinterpret_cast<uintptr_t>(out_tables)) & 15u) != 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_lut_build: pivots and output tables must be 16-byte aligned.");
     TANN_CUDA(tann::LaunchLutBuild(tables_col_major, centroid, chunk_offsets, dim, num_chunks, queries,
                                    query_kind, num_queries, out_tables, (cudaStream_t)stream));
     return TANN_OK;
@@ -178,6 +181,8 @@ TannStatus tann_beam_search(const TannIndexView* index, const TannBeamParams* pa
             return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: queries are needed when no table is given.");
         if (!index->pq_tables_col_major || !index->pq_centroid || !index->pq_chunk_offsets)
             return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: PQ index must be loaded before search.");
+        if ((reinterpret_cast<uintptr_t>(index->pq_tables_col_major) & 15u) != 0)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: PQ pivots must be 16-byte aligned.");
     }
     if (!entry_offsets || !entry_ids || !out_candidates || !out_stats)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: null pointer.");

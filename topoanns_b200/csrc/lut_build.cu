@@ -16,21 +16,29 @@ lut_build_kernel(const float* __restrict__ tables_col_major, const float* __rest
     extern __shared__ float lut_smem[];
     float* sq = lut_smem;                                       // [dim]
     uint32_t* offs = reinterpret_cast<uint32_t*>(sq + dim);     // [M + 1]
-    for (uint32_t i = threadIdx.x; i <= M; i += kLutThreads) offs[i] = chunk_offsets[i];
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t i = tid; i <= M; i += kLutThreads) offs[i] = chunk_offsets[i];
+    // chunks of equal width (the usual case) take the unrolled build: four centroids per thread and
+    // 16 sixteen-byte loads in flight; the entries are written straight to their place in the output
+    const uint32_t sub0 = __ldg(chunk_offsets + 1) - __ldg(chunk_offsets);
+    bool same = __ldg(chunk_offsets) == 0u;
+    for (uint32_t i = tid; i < M; i += kLutThreads)
+        same = same && (__ldg(chunk_offsets + i + 1) - __ldg(chunk_offsets + i)) == sub0;
+    const uint32_t uniform_sub = __syncthreads_and(same) ? sub0 : 0u;
     for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
         __syncthreads();
-        for (uint32_t i = threadIdx.x; i < dim; i += kLutThreads)
+        for (uint32_t i = tid; i < dim; i += kLutThreads)
             sq[i] = LoadAsFloat<float>(queries, query_kind, q * dim + i) - centroid[i];
         __syncthreads();
         float* o = out + q * (uint64_t)M * kCentroids;
-        for (uint32_t e = threadIdx.x; e < M * kCentroids; e += kLutThreads) {
-            const uint32_t m = e >> 8, c = e & 255u;
-            float acc = 0.0f;
-            for (uint32_t k = offs[m]; k < offs[m + 1]; ++k) {
-                const float diff = __ldg(tables_col_major + (size_t)k * kCentroids + c) - sq[k];
-                acc = fmaf(diff, diff, acc);
-            }
-            o[e] = acc;
+        switch (uniform_sub) {
+            case 1: BuildLutUniform<1, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            case 2: BuildLutUniform<2, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            case 3: BuildLutUniform<3, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            case 4: BuildLutUniform<4, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            case 6: BuildLutUniform<6, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            case 8: BuildLutUniform<8, kLutThreads>(o, sq, tables_col_major, M, tid); break;
+            default: BuildLutGeneric<kLutThreads>(o, sq, offs, tables_col_major, M, tid); break;
         }
     }
 }

@@ -110,6 +110,67 @@ __device__ __forceinline__ unsigned long long WarpSortKey(unsigned long long k, 
     return k;
 }
 
+// Query look-up table (src/search/pq_query_tables.cu:33-52), four consecutive centroids per thread
+// and step: one 16-byte load per dim and the same per-entry FMA chain (ascending dim) as the
+// one-entry form. kSub = dims per chunk when every chunk has that many: the loads of a step
+// (sixteen per thread) are then all issued before the first is used, which is what keeps the
+// 128 KB table stream from L2 from being latency-bound.
+template <int kSub, int kThreads>
+__device__ __forceinline__ void BuildLutUniform(float* lut /*shared or global, 16-byte aligned*/, const float* sq, const float* tables,
+                                                uint32_t M, uint32_t tid) {
+    constexpr int kItems = kSub <= 2 ? 8 : (kSub <= 4 ? 4 : 2);   // 16 loads in flight per thread
+    const uint32_t total = M * (kCentroids / 4);
+    for (uint32_t item0 = tid; item0 < total; item0 += kThreads * kItems) {
+        float4 t[kItems][kSub];
+#pragma unroll
+        for (int u = 0; u < kItems; ++u) {
+            const uint32_t item = item0 + u * kThreads;
+            if (item < total) {
+                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+#pragma unroll
+                for (int sd = 0; sd < kSub; ++sd)
+                    t[u][sd] = __ldg(reinterpret_cast<const float4*>(
+                        tables + (size_t)(m * kSub + sd) * kCentroids + c4));
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kItems; ++u) {
+            const uint32_t item = item0 + u * kThreads;
+            if (item < total) {
+                const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int sd = 0; sd < kSub; ++sd) {
+                    const float sv = sq[m * kSub + sd];
+                    float df = t[u][sd].x - sv; acc.x = fmaf(df, df, acc.x);
+                    df = t[u][sd].y - sv; acc.y = fmaf(df, df, acc.y);
+                    df = t[u][sd].z - sv; acc.z = fmaf(df, df, acc.z);
+                    df = t[u][sd].w - sv; acc.w = fmaf(df, df, acc.w);
+                }
+                *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
+            }
+        }
+    }
+}
+
+template <int kThreads>
+__device__ __noinline__ void BuildLutGeneric(float* lut, const float* sq, const uint32_t* offs,
+                                             const float* tables, uint32_t M, uint32_t tid) {
+    for (uint32_t item = tid; item < M * (kCentroids / 4); item += kThreads) {
+        const uint32_t m = item >> 6, c4 = (item & 63u) * 4u;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t dim = offs[m]; dim < offs[m + 1]; ++dim) {
+            const float4 t = __ldg(reinterpret_cast<const float4*>(tables + (size_t)dim * kCentroids + c4));
+            const float sv = sq[dim];
+            float df = t.x - sv; acc.x = fmaf(df, df, acc.x);
+            df = t.y - sv; acc.y = fmaf(df, df, acc.y);
+            df = t.z - sv; acc.z = fmaf(df, df, acc.z);
+            df = t.w - sv; acc.w = fmaf(df, df, acc.w);
+        }
+        *reinterpret_cast<float4*>(lut + m * kCentroids + c4) = acc;
+    }
+}
+
 // ---- bulk asynchronous copy (TMA, untiled form) of a contiguous global range into shared memory ----
 // One thread arms an mbarrier with the byte count and issues the copies; every thread then polls the
 // barrier's phase. Source, destination and size are multiples of 16 bytes. The poll is bounded: if the
