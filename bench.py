@@ -57,6 +57,10 @@ def parse_args():
     ap.add_argument("--top-n", type=int, default=0, help="with --top-l: rerank top_n (default 32)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sharded", action="store_true",
+                    help="N > 1 only: instead of replicas, split the index by node-id range over the GPUs (--nodes per "
+                         "GPU, R = 32 records as in the 1 B-vector configuration); every rank searches its own 10 k "
+                         "queries and reads (N-1)/N of all rows from its peers over NVLink")
     return ap.parse_args()
 
 
@@ -183,12 +187,29 @@ def main():
     device = f"cuda:{local}" if use_cuda else "cpu"
 
     from topoanns_b200 import synth
-    s, build_s = build_index(args, device)
-    gt = s.gt_ids.cpu().numpy()
+    sharded = args.sharded and world > 1 and args.impl == "b200"
+    peer_buffers = None
+    if sharded:
+        from topoanns_b200 import sharding, synth_sharded
+        t0 = time.time()
+        cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=args.nodes * world, num_queries=args.queries * world,
+                                  components=max(world, args.nodes * world // 1000), kmeans_iters=5, train_sample=65536)
+        s = synth_sharded.build(cfg, device)       # this rank's shard + the whole query set and ground truth
+        build_s = time.time() - t0
+        b, e = sharding.query_shard(s.queries.shape[0], world, rank)
+        queries_all, gt = s.queries, s.gt_ids.cpu().numpy()[b:e]
+        s.queries = queries_all[b:e].contiguous()  # every rank serves its own slice
+        degree, M = s.adjacency.shape[1], s.pq_codes.shape[1]
+        workload = (f"cfg4-style shards: {s.total_nodes} x {cfg.dim} uint8 over {world} GPUs ({s.rows_per_shard} per GPU), "
+                    f"R={degree}, PQ M={M}x256, RVQ entries=128, {args.queries} queries/batch per GPU, k=10, W=2, "
+                    f"{world - 1}/{world} of the row gathers remote (NVLink peer loads)")
+    else:
+        s, build_s = build_index(args, device)
+        gt = s.gt_ids.cpu().numpy()
+        degree, M = s.adjacency.shape[1], s.pq_codes.shape[1]
+        workload = (f"cfg2: {s.vectors.shape[0]} x {s.cfg.dim} uint8, R={degree}, PQ M={M}x256, RVQ 256x256 entries=128, "
+                    f"{s.queries.shape[0]} queries/batch, k=10, W=2, max_expansions=4096")
     Q = s.queries.shape[0]
-    degree, M = s.adjacency.shape[1], s.pq_codes.shape[1]
-    workload = (f"cfg2: {s.vectors.shape[0]} x {s.cfg.dim} uint8, R={degree}, PQ M={M}x256, RVQ 256x256 entries=128, "
-                f"{Q} queries/batch, k=10, W=2, max_expansions=4096")
 
     if args.impl == "reference":
         # the operating point the CUDA arm's sweep settles on for this seeded workload
@@ -207,8 +228,13 @@ def main():
 
     from topoanns_b200 import capi, search
     lib = capi.load()
-    ix = search.device_index_from_synth(s, device)
-    model = search.rvq_model_from_synth(s, device)
+    if sharded:
+        ix, peer_buffers = sharding.peer_index_from_sharded(s)
+        model = search.RvqModel(dim=s.cfg.dim, coarse=s.rvq_coarse.contiguous(), fine=s.rvq_fine.contiguous(),
+                                bucket_sizes=s.rvq_buckets[0], cluster_offsets=s.rvq_buckets[1], cluster_ids=s.rvq_buckets[2])
+    else:
+        ix = search.device_index_from_synth(s, device)
+        model = search.rvq_model_from_synth(s, device)
     max_cap = 1024
     sr = search.Searcher(ix, Q, max_cap, max(TOPN_SWEEP), 128)
     sr.set_rvq(model, 128)
@@ -319,8 +345,13 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms, beam_ms = [float(x) for x in times.cpu()]
     if rank != 0:
+        sr.close()
         if world > 1:
             import torch.distributed as dist
+            if peer_buffers is not None:
+                dist.barrier()
+                for pb in peer_buffers.values():
+                    pb.close()
             dist.destroy_process_group()
         return 0
 
@@ -330,16 +361,19 @@ def main():
     else:
         peak, peak_src = 6650.0, "fallback"
     achieved = beam_bytes / (beam_ms * 1e-3) / 1e9
-    traffic = NCU_BEAM_TRAFFIC_BYTES.get((L, cap)) if (args.nodes, Q) == (10_000_000, 10_000) else None
+    traffic = NCU_BEAM_TRAFFIC_BYTES.get((L, cap)) if (args.nodes, Q) == (10_000_000, 10_000) and not sharded else None
     rec = synth.recall_at_k(ids, gt, 10)
     total_q = Q * world * args.steps
     line = {
-        "metric": "QPS at recall@10>=0.95 (10M uint8 d=128, 1 batch of 10k queries per GPU)",
+        "metric": ("QPS at recall@10>=0.95 (uint8 d=128 index sharded by node-id range, 1 batch of 10k queries per GPU)"
+                   if sharded else "QPS at recall@10>=0.95 (10M uint8 d=128, 1 batch of 10k queries per GPU)"),
         "value": total_q / (dev_ms * 1e-3), "unit": "queries/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "u8", "data": "synthetic",
         "config": {"workload": workload, "top_l": L, "rerank_top_n": top_n, "recall_at_10": round(rec, 4),
-                   "recall_target_met": bool(rec >= RECALL_TARGET), "parallelism": f"replica x{world}, queries sharded",
+                   "recall_target_met": bool(rec >= RECALL_TARGET),
+                   "parallelism": (f"node-id-range shards x{world}, queries sharded" if sharded
+                                   else f"replica x{world}, queries sharded"),
                    "l2_policy": "index (4.2 GB) and per-step gathers exceed the 126 MB L2; no flush",
                    "index_build_s": round(build_s, 1), "sweep": sweep,
                    "beam_kernel": {"smem_bytes": smem, "blocks_per_sm": blocks_per_sm, "resident_blocks": grid, "grid": "one block per query",
@@ -363,6 +397,10 @@ def main():
     sr.close()
     if world > 1:
         import torch.distributed as dist
+        if peer_buffers is not None:
+            dist.barrier()
+            for pb in peer_buffers.values():
+                pb.close()
         dist.destroy_process_group()
     return 0
 
