@@ -279,6 +279,9 @@ TannStatus tann_enable_peer_access(int peer_device);
  * optional pq2 refine / bound filter, exact rerank and top-k packing, and copies ids and
  * distances back. It is what TopoAnnsSearch::RunBatchFloat32Fused does
  * (src/search/topoanns_search.cpp:330-344) minus the per-query host materialisation.
+ * Page-locked caller buffers (cudaHostAlloc / cudaHostRegister) are copied from and to directly,
+ * pageable ones go through the searcher's pinned staging buffers. With a pq2 view attached the
+ * second-level table entries are computed inside the refine kernel (no Q x M x 256 table is built).
  */
 typedef struct TannRvqModelView {
     uint32_t dim, num_coarse, num_fine, entry_count;
