@@ -1,4 +1,5 @@
-// Fused Bloom-filtered beam search, one query per 128-thread block, persistent over the batch.
+// Fused Bloom-filtered beam search, one query per 128-thread block (the grid is the batch; the loop over
+// queries only matters when a caller launches fewer blocks than queries).
 //
 // What it computes is the traversal of the reference kernel
 // (src/search/topology_search_kernel.cu:2190-2664): same Bloom filter (hashes :382-385,611-653,
