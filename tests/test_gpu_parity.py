@@ -141,7 +141,7 @@ def test_lut_matches_checker_all_query_kinds():
         assert np.array_equal(got, want)  # same FMA order on both sides
 
 
-@pytest.mark.parametrize("top_l,width", [(16, 1), (64, 2), (100, 2), (256, 4)])
+@pytest.mark.parametrize("top_l,width", [(16, 1), (64, 2), (100, 2), (256, 4), (1100, 2)])
 def test_beam_search_matches_checker(top_l, width):
     s, host = small_index()
     ix = device_index(s)
