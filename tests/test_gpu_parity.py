@@ -559,6 +559,48 @@ def test_sharded_and_cached_providers_give_the_same_result():
         capi.check(lib.tann_host_free(hp))
 
 
+def test_wide_float_configuration_with_pinned_host_vectors():
+    """The 768-dimensional float configuration in miniature: M = 96 chunks of 8 dims (the widest specialised
+    table), 3 KB vectors at one per page, vector pages in mapped pinned host memory read over UVA, RVQ entries."""
+    s, host = small_index(name="cfg5", num_nodes=6000, components=12, num_queries=64)
+    assert s.vectors.shape[1] == 768 and s.pq_codes.shape[1] == 96
+    ix = device_index(s)
+    q = s.queries.cuda().contiguous()
+    Q = q.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid, 17])
+    p = search.TopologySearchParams(top_l=128, search_width=2, max_expansions=4096)
+    cap = p.capacity(64)
+    cand, stats = search.beam_search(ix, p, eo, ei, queries=q, capacity=cap)
+    lut_ref = orc.lut_build(s.queries.cpu().numpy(), host["pq_tables"], host["pq_centroid"], host["pq_chunk_offsets"])
+    ref_cand, ref_stats = orc.beam_search(host["adjacency"], host["codes"], lut_ref, np_u32(eo), np_u32(ei), top_l=128,
+                                          search_width=2, max_expansions=4096, capacity=cap)
+    assert_candidates_equal(cand, stats, ref_cand, ref_stats)
+    rp = search.RerankExactParams(top_k=10, top_n=64)
+    rd, ri, rn, _ = orc.rerank(ref_cand, s.queries.cpu().numpy(), host_pages(host), np.float32, top_n=64, top_k=10,
+                               vectors_per_page=host["vpp"], page_bytes=4096, vector_bytes=host["vb"])
+    lib = capi.load()
+    nbytes = ix.vector_pages.numel()
+    hp, dp = C.c_void_p(), C.c_void_p()
+    capi.check(lib.tann_host_alloc_mapped(nbytes, C.byref(hp), C.byref(dp)))
+    try:
+        pages_host = ix.vector_pages.cpu().numpy()          # keep the array alive across the copy
+        C.memmove(hp.value, pages_host.ctypes.data, nbytes)
+        hosted = search.DeviceIndex(
+            num_nodes=ix.num_nodes, degree=ix.degree, dim=ix.dim, vector_kind=ix.vector_kind, adjacency=ix.adjacency,
+            codes=ix.codes, pq_tables_col_major=ix.pq_tables_col_major, pq_centroid=ix.pq_centroid,
+            pq_chunk_offsets=ix.pq_chunk_offsets, vector_bytes=ix.vector_bytes, vectors_per_page=ix.vectors_per_page,
+            vector_bases=[dp.value])
+        for index in (ix, hosted):
+            d, i, n_exact, _ = search.rerank_exact(index, rp, cand, q)
+            torch.cuda.synchronize()
+            assert n_exact == rn
+            assert np.array_equal(np_u32(i), ri)
+            assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
+    finally:
+        torch.cuda.synchronize()
+        capi.check(lib.tann_host_free(hp))
+
+
 def test_parameter_errors_are_reported():
     s, _ = small_index()
     ix = device_index(s)
