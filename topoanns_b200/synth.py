@@ -124,7 +124,11 @@ def _sample_component(cfg: SynthConfig, centres, comp_ids, gen, basis=None):
     n = comp_ids.shape[0]
     if cfg.low_rank > 0:
         z = torch.randn((n, cfg.low_rank), generator=gen, device=dev)
-        x = centres[comp_ids] + (z.unsqueeze(1) @ basis[comp_ids % basis.shape[0]]).squeeze(1) * cfg.sigma
+        x = centres[comp_ids]
+        step = 8192   # the gathered bases are [step, rank, dim] floats: bounded, whatever n is
+        for b in range(0, n, step):
+            e = min(n, b + step)
+            x[b:e] += (z[b:e].unsqueeze(1) @ basis[comp_ids[b:e] % basis.shape[0]]).squeeze(1) * cfg.sigma
         x = x + torch.randn((n, cfg.dim), generator=gen, device=dev) * cfg.iso_sigma
     else:
         x = centres[comp_ids] + torch.randn((n, cfg.dim), generator=gen, device=dev) * cfg.sigma
