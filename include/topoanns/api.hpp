@@ -502,6 +502,13 @@ public:
     void AttachTopologyShards(const TannShards& adjacency);
     void AttachPqCodeShards(const TannShards& codes);
 
+    // Optional HBM layout with every node's neighbours' PQ codes next to each other (degree * M bytes per
+    // node): an expansion then reads adjacency ids and neighbour codes in one memory round trip. Results do
+    // not change. Needs the topology in HBM and the PQ index loaded; call again after either changes.
+    void BuildNeighborCodeLayout();
+    void DropNeighborCodeLayout() { neighbor_codes_.reset(); }
+    bool has_neighbor_code_layout() const { return static_cast<bool>(neighbor_codes_); }
+
     // The view the C ABI takes; `need_vectors` also resolves the attached provider's pages.
     TannIndexView MakeIndexView(bool need_vectors) const;
 
@@ -524,6 +531,7 @@ private:
     std::shared_ptr<VectorStore> vector_store_;
     bool has_adjacency_shards_ = false, has_code_shards_ = false;
     TannShards adjacency_shards_{}, code_shards_{};
+    std::shared_ptr<CudaBuffer<std::uint8_t>> neighbor_codes_;
 };
 
 // ---- traversal (reference: topology_search.hpp) ---------------------------------------------------------

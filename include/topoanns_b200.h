@@ -82,6 +82,14 @@ typedef struct TannIndexView {
     const float* pq_tables_col_major; /* dev, [dim][256] */
     const float* pq_centroid;         /* dev, [dim] */
     const uint32_t* pq_chunk_offsets; /* dev, [M + 1] */
+    /* Optional (base[0] == NULL = absent): the PQ codes of every node's neighbours stored next to each
+     * other in adjacency order, rows of degree * num_chunks bytes sharded like `adjacency`. With it an
+     * expansion reads its neighbours' codes from one contiguous row whose address is known together
+     * with the adjacency row's, so both arrive in one memory round trip instead of two dependent ones.
+     * Costs degree * num_chunks bytes per node of HBM (2 KB at R = 64, M = 32); results are identical.
+     * No counterpart in the reference's resident layout (its disk layout co-locates node data,
+     * include/topoanns/topology_search.hpp:27-28 combined_node_bytes). */
+    TannShards neighbor_codes;
 } TannIndexView;
 
 /* Folded learned traversal-stop model, src/search/topology_search_kernel.cu:98-112,327-380. */
@@ -258,6 +266,13 @@ TannStatus tann_rerank_topk_static(const TannIndexView* index, const TannRerankP
                                    uint32_t query_kind, const float* error_bounds /*dev [N] or NULL*/,
                                    float* out_dists /*dev [Q][top_k]*/, uint32_t* out_ids /*dev [Q][top_k]*/,
                                    tann_stream_t stream);
+
+/* Fills rows [first_node, first_node + num_rows) of the optional neighbour-code layout
+ * (TannIndexView::neighbor_codes): out[row][j][0..M) = codes[adjacency[first_node + row][j]], zeros for padding
+ * slots. `out` is dev, num_rows * degree * num_chunks bytes, 16-byte aligned; a rank of a sharded index builds its
+ * own node range (peer code rows are read over NVLink). No counterpart in the reference. */
+TannStatus tann_neighbor_codes_build(const TannIndexView* index, uint64_t first_node, uint64_t num_rows,
+                                     void* out /*dev*/, tann_stream_t stream);
 
 /* ---- memory helpers for the providers (HBM-resident, NVLink-peer, pinned-host / UVA) -------- */
 TannStatus tann_device_alloc(uint64_t bytes, void** out_dev);

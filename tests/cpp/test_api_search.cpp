@@ -235,6 +235,21 @@ void TestRerankAndEndToEnd() {
         ep.rerank.mode = RerankExecutionMode::kLinear;
         CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, ep));
     }
+    // the neighbour-code layout changes where the code rows are read from, not what is found
+    {
+        r.BuildNeighborCodeLayout();
+        CHECK_TRUE(r.has_neighbor_code_layout());
+        const auto inl = TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, params);
+        for (int q = 0; q < 2; ++q) {
+            CHECK_EQ(inl.queries[q].topology.stats.visited_nodes, base.queries[q].topology.stats.visited_nodes);
+            CHECK_EQ(inl.queries[q].topology.stats.expanded_nodes, base.queries[q].topology.stats.expanded_nodes);
+            for (std::size_t i = 0; i < 2; ++i) {
+                CHECK_EQ(inl.queries[q].rerank.topk[i].node_id, base.queries[q].rerank.topk[i].node_id);
+                CHECK_EQ(inl.queries[q].rerank.topk[i].distance, base.queries[q].rerank.topk[i].distance);
+            }
+        }
+        r.DropNeighborCodeLayout();
+    }
     // the pinned-host page provider gives the same fused result
     r.AttachVectorPageProvider(std::make_shared<PinnedHostVectorPageProvider>(fx::Tmp("e2e_vectors.ssd")));
     const auto hosted = TopoAnnsSearch::RunBatchFloat32Fused(r, dev_entries, queries, 2, params);

@@ -35,7 +35,7 @@ def test_struct_sizes_match_the_header():
     assert C.sizeof(capi.LearnedStop) == 6 * 4 + 32 * 4 + 12 * 4 + 12 * 4 + 3 * 4
     assert C.sizeof(capi.BeamParams) == 8 * 4 + C.sizeof(capi.LearnedStop)
     assert C.sizeof(capi.RerankParams) == 32
-    assert C.sizeof(capi.IndexView) == 8 + 16 + 24 + 3 * C.sizeof(capi.Shards) + 16 + 24
+    assert C.sizeof(capi.IndexView) == 8 + 16 + 24 + 3 * C.sizeof(capi.Shards) + 16 + 24 + C.sizeof(capi.Shards)
 
 
 def test_parameter_checks_answer_without_a_gpu():

@@ -601,6 +601,42 @@ def test_wide_float_configuration_with_pinned_host_vectors():
         capi.check(lib.tann_host_free(hp))
 
 
+def test_neighbor_code_layout_gives_identical_results():
+    """The optional layout that stores every node's neighbours' PQ codes next to each other only changes
+    where the code rows are read from: candidates and statistics stay bit-identical, also with padded
+    adjacency rows and through the searcher."""
+    s, host = small_index()
+    ix = device_index(s)
+    q = s.queries.cuda().contiguous()
+    Q = q.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid, 3])
+    inl = search.inline_neighbor_codes(device_index(s))
+    assert inl.neighbor_codes.shape == (ix.num_nodes, ix.degree, ix.num_chunks)
+    for top_l, width in ((64, 2), (16, 1), (256, 4)):
+        p = search.TopologySearchParams(top_l=top_l, search_width=width, max_expansions=4096)
+        cand, stats = search.beam_search(ix, p, eo, ei, queries=q)
+        cand2, stats2 = search.beam_search(inl, p, eo, ei, queries=q)
+        assert torch.equal(cand, cand2) and torch.equal(stats, stats2)
+    # padded rows (0xffffffff slots) and the whole path
+    pad = search.device_index_from_arrays(adjacency=formats.pad_degree(host["adjacency"], 64), codes=host["codes"],
+                                          vectors=host["vectors"], pq_tables_row_major=host["pq_tables"],
+                                          pq_centroid=host["pq_centroid"], pq_chunk_offsets=host["pq_chunk_offsets"])
+    p = search.TopologySearchParams(top_l=64, search_width=2, max_expansions=4096)
+    base_cand, base_stats = search.beam_search(pad, p, eo, ei, queries=q)
+    search.inline_neighbor_codes(pad)
+    cand3, stats3 = search.beam_search(pad, p, eo, ei, queries=q)
+    assert torch.equal(base_cand, cand3) and torch.equal(base_stats, stats3)
+    sr = search.Searcher(inl, Q, 128, 64, 128)
+    sr2 = search.Searcher(ix, Q, 128, 64, 128)
+    rp = search.RerankExactParams(top_k=10, top_n=32)
+    fe = np.array([s.medoid, 3], np.uint32)
+    ids_a, d_a, st_a = sr.run_host(s.queries.cpu().numpy(), p, rp, fixed_entries=fe, want_stats=True)
+    ids_b, d_b, st_b = sr2.run_host(s.queries.cpu().numpy(), p, rp, fixed_entries=fe, want_stats=True)
+    assert np.array_equal(ids_a, ids_b) and np.array_equal(d_a, d_b) and np.array_equal(st_a, st_b)
+    sr.close()
+    sr2.close()
+
+
 def test_parameter_errors_are_reported():
     s, _ = small_index()
     ix = device_index(s)

@@ -37,7 +37,7 @@ class IndexView(C.Structure):
         ("vectors_per_page", C.c_uint64), ("page_bytes", C.c_uint64), ("adjacency", Shards),
         ("codes", Shards), ("vectors", Shards), ("adjacency_cache", C.c_void_p),
         ("adjacency_cached_rows", C.c_uint64), ("pq_tables_col_major", C.c_void_p),
-        ("pq_centroid", C.c_void_p), ("pq_chunk_offsets", C.c_void_p),
+        ("pq_centroid", C.c_void_p), ("pq_chunk_offsets", C.c_void_p), ("neighbor_codes", Shards),
     ]
 
 
@@ -107,6 +107,7 @@ SIGNATURES = {
     "tann_topk_pack": (_I, [_VP, _VP, _U64, _U32, _U32, _VP, _VP, _VP]),
     "tann_rerank_topk_static": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                      _VP, _VP, _VP, _VP]),
+    "tann_neighbor_codes_build": (_I, [C.POINTER(IndexView), _U64, _U64, _VP, _VP]),
     "tann_device_alloc": (_I, [_U64, C.POINTER(_VP)]),
     "tann_device_free": (_I, [_VP]),
     "tann_host_alloc_mapped": (_I, [_U64, C.POINTER(_VP), C.POINTER(_VP)]),

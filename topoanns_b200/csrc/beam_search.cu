@@ -542,6 +542,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
             for (uint32_t r = 0; r < rounds; ++r) {
                 const uint32_t s = r * kBeamThreads + tid;
                 uint32_t id = kInvalid;
+                bool codes_requested = false;   // kSingle: my_words already on their way (neighbour-code layout)
                 if (s < nslots) {
                     if (in_entries) {
                         const uint64_t e = (uint64_t)batch * slots + s;
@@ -556,6 +557,14 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                                 : reinterpret_cast<const uint32_t*>(
                                       ShardRow(a.ix.adjacency, node, (uint64_t)deg * 4));
                         id = __ldg(row + j);
+                        // With the neighbour-code layout the slot's code row sits at (node, j): its address
+                        // does not depend on the id just requested, so both loads share one round trip.
+                        if constexpr (kSingle && kM > 0) {
+                            if (a.ix.neighbor_codes.base[0] != nullptr) {
+                                LoadCodeWords<kM>(ShardRow(a.ix.neighbor_codes, node, (uint64_t)deg * kM) + (size_t)j * kM, my_words);
+                                codes_requested = true;
+                            }
+                        }
                     }
                 }
                 const BloomBits bits = BloomPositions(id);
@@ -563,7 +572,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (kSingle) my_bits = bits;
                 // The code row does not depend on the barrier below: request it now.
                 if constexpr (kSingle && kM > 0)
-                    if (pass) LoadCodeWords<kM>(ShardRow(a.ix.codes, id, M), my_words);
+                    if (pass && !codes_requested) LoadCodeWords<kM>(ShardRow(a.ix.codes, id, M), my_words);
                 // Park the surviving id in the key slot; phase 2 turns it into a key.
                 const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
                 if (kSingle) {

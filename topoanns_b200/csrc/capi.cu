@@ -329,6 +329,23 @@ TannStatus tann_topk_pack(const float* dists, const uint32_t* ids, uint64_t num_
     return TANN_OK;
 }
 
+TannStatus tann_neighbor_codes_build(const TannIndexView* index, uint64_t first_node, uint64_t num_rows,
+                                     void* out, tann_stream_t stream) {
+    if (!index || !out) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_neighbor_codes_build: null pointer.");
+    if (index->degree == 0 || index->num_chunks == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_neighbor_codes_build: topology and PQ index must be loaded.");
+    if (first_node + num_rows > index->num_nodes)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_neighbor_codes_build: rows beyond the index.");
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) != 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_neighbor_codes_build: output must be 16-byte aligned.");
+    TannStatus st = CheckShards(index->adjacency, index->num_nodes, "adjacency");
+    if (st != TANN_OK) return st;
+    st = CheckShards(index->codes, index->num_nodes, "codes");
+    if (st != TANN_OK) return st;
+    TANN_CUDA(tann::LaunchNeighborCodes(*index, first_node, num_rows, static_cast<uint8_t*>(out), (cudaStream_t)stream));
+    return TANN_OK;
+}
+
 // ---- memory helpers ---------------------------------------------------------------------------
 
 TannStatus tann_device_alloc(uint64_t bytes, void** out_dev) {

@@ -55,6 +55,9 @@ cudaError_t LaunchF32ToU8Checked(const float* src, uint64_t n, uint8_t* dst, uin
 cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, uint32_t top_n,
                            uint32_t top_k, float* out_dists, uint32_t* out_ids, cudaStream_t stream);
 
+cudaError_t LaunchNeighborCodes(const TannIndexView& ix, uint64_t first_node, uint64_t num_rows, uint8_t* out,
+                                cudaStream_t stream);
+
 int SmCount();
 
 }  // namespace tann

@@ -427,6 +427,20 @@ void SearchResources::AttachPqCodeShards(const TannShards& codes) {
     has_code_shards_ = true;
 }
 
+void SearchResources::BuildNeighborCodeLayout() {
+    const char* ctx = "BuildNeighborCodeLayout";
+    if (!pq_index_) throw std::runtime_error(BuildErrorMessage(ctx, "PQ index must be loaded first."));
+    if (has_adjacency_shards_ || has_code_shards_ || topology_->residency() != TopologyResidency::kHbm)
+        throw std::runtime_error(BuildErrorMessage(ctx, "the layout is built for an HBM-resident, unsharded index."));
+    neighbor_codes_.reset();
+    const TannIndexView view = MakeIndexView(false);
+    const std::size_t bytes = static_cast<std::size_t>(view.num_nodes) * view.degree * view.num_chunks;
+    auto buffer = std::make_shared<CudaBuffer<std::uint8_t>>(CudaBuffer<std::uint8_t>::Allocate(bytes));
+    ThrowIfTannError(tann_neighbor_codes_build(&view, 0, view.num_nodes, buffer->get(), nullptr), ctx);
+    ThrowIfCudaError(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    neighbor_codes_ = std::move(buffer);
+}
+
 TannIndexView SearchResources::MakeIndexView(bool need_vectors) const {
     TannIndexView v{};
     v.num_nodes = topology_->num_nodes();
@@ -448,6 +462,7 @@ TannIndexView SearchResources::MakeIndexView(bool need_vectors) const {
         v.pq_tables_col_major = pq.device().tables_col_major.get();
         v.pq_centroid = pq.device().centroid.get();
         v.pq_chunk_offsets = pq.device().chunk_offsets.get();
+        if (neighbor_codes_) v.neighbor_codes = OneShard(neighbor_codes_->get());
     }
     if (need_vectors && vector_store_) {
         const VectorStoreHeader& h = vector_store_->header;

@@ -37,6 +37,7 @@ struct Args {
     std::string vector_residency = "hbm", topology_residency = "hbm";
     std::uint64_t topology_cached_rows = 0;
     std::size_t repeats = 1;
+    bool neighbor_code_layout = false;
 };
 
 struct FloatMatrix { std::uint32_t rows = 0, cols = 0; std::vector<float> values; };
@@ -57,7 +58,7 @@ struct SweepPoint {
                  " --rerank-use-pq2] [--rerank-use-pq2-bound-filter] [--rerank-use-early-stop]"
                  " [--rerank-early-stop-min-prefix <count>] [--rerank-early-stop-patience-tiles <count>] [--max-expansions <count>] [--rvq-entry-count <count>]"
                  " [--vector-residency <hbm|pinned-host>] [--topology-residency <hbm|pinned-host>]"
-                 " [--topology-cached-rows <count>] [--repeats <count>]"
+                 " [--topology-cached-rows <count>] [--repeats <count>] [--neighbor-code-layout]"
                  " (flags of the NVMe backend, --bam-*, --frontier-pq-modes and the learned rerank stop flags are accepted"
                  " and ignored)"
               << std::endl;
@@ -140,6 +141,7 @@ Args Parse(int argc, char** argv) {
         else if (f == "--topology-residency") a.topology_residency = value();
         else if (f == "--topology-cached-rows") a.topology_cached_rows = std::stoull(value());
         else if (f == "--repeats") a.repeats = std::max<std::size_t>(1, std::stoull(value()));
+        else if (f == "--neighbor-code-layout") a.neighbor_code_layout = true;
         else { std::cerr << "Unknown flag: " << f << std::endl; Usage(); }
     }
     if (a.index_dir.empty() || a.rvq_model.empty() || a.query_bin.empty() || a.num_queries == 0 || a.top_l_values.empty())
@@ -217,6 +219,7 @@ int main(int argc, char** argv) {
             resources.AttachVectorPageProvider(std::make_shared<topoanns::HbmVectorPageProvider>(args.index_dir / "vectors.ssd"));
         if (args.topology_residency == "pinned-host")
             resources.mutable_topology().SetResidency(topoanns::TopologyResidency::kPinnedHost, args.topology_cached_rows);
+        if (args.neighbor_code_layout) resources.BuildNeighborCodeLayout();
         if (resources.vector_store_header().dim != queries.cols) throw std::runtime_error("Query dim and vector store dim do not match.");
         topoanns::RvqModel rvq_model = topoanns::RvqModel::Load(args.rvq_model);
         if (rvq_model.dim() != queries.cols) throw std::runtime_error("RVQ model dim and query dim do not match.");

@@ -39,6 +39,8 @@ def main() -> None:
     ap.add_argument("--entries", type=int, default=128)
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--staged-table", action="store_true", help="build the query tables with tann_lut_build first")
+    ap.add_argument("--inline-neighbor-codes", action="store_true",
+                    help="also store every node's neighbours' PQ codes next to each other (degree * M bytes per node)")
     ap.add_argument("--topology", default="hbm", choices=["hbm", "pinned-host"],
                     help="where the adjacency lists live (pinned-host = mapped host memory read over PCIe)")
     ap.add_argument("--cached-fraction", type=float, default=0.0,
@@ -49,6 +51,9 @@ def main() -> None:
     s = synth.build(cfg, "cuda")
     ix = search.device_index_from_synth(s)
     q = s.queries.cuda().contiguous()
+    if a.inline_neighbor_codes:
+        search.inline_neighbor_codes(ix)
+        print(f"neighbour-code layout: {ix.neighbor_codes.numel() / 1e9:.2f} GB")
     host_alloc = None
     if a.topology == "pinned-host":
         import ctypes as C

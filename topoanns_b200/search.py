@@ -106,6 +106,9 @@ class DeviceIndex:
     rows_per_shard: int = 0
     adjacency_cache: Optional[torch.Tensor] = None
     adjacency_cached_rows: int = 0
+    # optional [N, degree, M] uint8: every node's neighbours' PQ codes in adjacency order (see inline_neighbor_codes)
+    neighbor_codes: Optional[torch.Tensor] = None
+    neighbor_codes_bases: Optional[Sequence[int]] = None
     keepalive: list = field(default_factory=list)
 
     @property
@@ -132,7 +135,21 @@ class DeviceIndex:
         v.pq_tables_col_major = self.pq_tables_col_major.data_ptr()
         v.pq_centroid = self.pq_centroid.data_ptr()
         v.pq_chunk_offsets = self.pq_chunk_offsets.data_ptr()
+        if self.neighbor_codes_bases or self.neighbor_codes is not None:
+            v.neighbor_codes = make_shards(self.neighbor_codes_bases or [self.neighbor_codes.data_ptr()], self.rows_per_shard)
         return v
+
+
+def inline_neighbor_codes(index: DeviceIndex) -> DeviceIndex:
+    """Adds the neighbour-code layout to an index held by this device: neighbor_codes[n, j] = codes[adjacency[n, j]]
+    (zeros for padding slots), built by the library's gather kernel. degree * M bytes per node; the search
+    results do not change."""
+    dev = index.pq_centroid.device
+    out = torch.empty((index.num_nodes, index.degree, index.num_chunks), dtype=torch.uint8, device=dev)
+    view = index.view()
+    capi.check(capi.load().tann_neighbor_codes_build(C.byref(view), 0, index.num_nodes, _ptr(out), _stream_ptr()))
+    index.neighbor_codes = out
+    return index
 
 
 def kind_of(t: torch.Tensor) -> int:
