@@ -724,6 +724,11 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                                 const uint8_t* row = static_cast<const uint8_t*>(a.ix.adjacency.base[0]) + (uint64_t)node * deg * 4;
                                 for (uint32_t off = 0; off < deg * 4; off += 128)
                                     asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
+                                if (a.ix.neighbor_codes.base[0] != nullptr) {
+                                    const uint8_t* crow = static_cast<const uint8_t*>(a.ix.neighbor_codes.base[0]) + (uint64_t)node * deg * M;
+                                    for (uint32_t off = 0; off < deg * M; off += 128)
+                                        asm volatile("prefetch.global.L2 [%0];" ::"l"(crow + off));
+                                }
                             }
                         }
                     }
