@@ -41,8 +41,8 @@ DEFAULT_POINT = (16, 192)   # (top_l, rerank_top_n): fastest sweep point with re
 # DRAM traffic of one beam_search_kernel launch (10 k queries, 10 M nodes), ncu dram__bytes_read.sum +
 # dram__bytes_write.sum, keyed by (top_l, candidate capacity) - the kernel does not depend on rerank_top_n
 # beyond the capacity it implies; summarised under profiles/.
-NCU_BEAM_TRAFFIC_BYTES_PLAIN = {(16, 256): 807.2e6}
-NCU_BEAM_TRAFFIC_BYTES_NEIGHBOR_CODES = {(16, 256): 544.0e6}
+NCU_BEAM_TRAFFIC_BYTES_PLAIN = {(16, 256): 749.9e6}
+NCU_BEAM_TRAFFIC_BYTES_NEIGHBOR_CODES = {(16, 256): 489.7e6}
 RECALL_TARGET = 0.95
 
 

@@ -18,7 +18,6 @@ struct BeamArgs {
     Cand* out_cand;
     uint32_t* out_stats;
     uint32_t* status;
-    uint32_t adjacency_in_local_hbm;  // 1: adjacency rows may be prefetched into L2 (one shard, this GPU's memory)
 };
 
 }  // namespace tann

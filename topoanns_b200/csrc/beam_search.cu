@@ -715,22 +715,6 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         }
                         nxt[rank + lo] = k;
                         if (rank + lo < a.p.learned_stop.top_k) ctl.ls_topk_changed = 1;
-                        // An entry that lands inside the top L will most likely be expanded within the
-                        // next pushes: ask L2 for its adjacency row now (a hint, results do not depend
-                        // on it), so that the selection's load does not wait for DRAM.
-                        if (rank + lo < L && a.adjacency_in_local_hbm) {
-                            const uint32_t node = (uint32_t)k;
-                            if (node >= a.ix.adjacency_cached_rows) {
-                                const uint8_t* row = static_cast<const uint8_t*>(a.ix.adjacency.base[0]) + (uint64_t)node * deg * 4;
-                                for (uint32_t off = 0; off < deg * 4; off += 128)
-                                    asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
-                                if (a.ix.neighbor_codes.base[0] != nullptr) {
-                                    const uint8_t* crow = static_cast<const uint8_t*>(a.ix.neighbor_codes.base[0]) + (uint64_t)node * deg * M;
-                                    for (uint32_t off = 0; off < deg * M; off += 128)
-                                        asm volatile("prefetch.global.L2 [%0];" ::"l"(crow + off));
-                                }
-                            }
-                        }
                     }
                 }
                 accepted = __syncthreads_count(pred);

@@ -43,19 +43,6 @@ bool IsPageLocked(const void* p) {
     return attr.type == cudaMemoryTypeHost;
 }
 
-// True when the array is one shard in the current device's own memory (not a peer's, not mapped host
-// memory): only then are L2 prefetches of its rows issued.
-bool IsLocalDeviceMemory(const TannShards& sh) {
-    if (sh.num_shards != 1 || sh.base[0] == nullptr) return false;
-    cudaPointerAttributes attr;
-    int dev = -1;
-    if (cudaPointerGetAttributes(&attr, sh.base[0]) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess) {
-        cudaGetLastError();
-        return false;
-    }
-    return attr.type == cudaMemoryTypeDevice && attr.device == dev;
-}
-
 uint32_t NextPow2(uint32_t v) {
     uint32_t p = 1;
     while (p < v) p <<= 1;
@@ -203,7 +190,6 @@ TannStatus tann_beam_search(const TannIndexView* index, const TannBeamParams* pa
     a.out_cand = static_cast<tann::Cand*>(out_candidates);
     a.out_stats = out_stats;
     a.status = status;
-    a.adjacency_in_local_hbm = IsLocalDeviceMemory(index->adjacency) ? 1u : 0u;
     TANN_CUDA(tann::LaunchBeam(a, plan.smem, plan.grid, (cudaStream_t)stream));
     return TANN_OK;
 }
