@@ -242,6 +242,63 @@ TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams*
                              unsigned long long* out_counts /*dev or NULL*/, uint32_t* status,
                              tann_stream_t stream);
 
+/* ---- learned rerank stop (the reference's persistent rerank, src/io/bam_vector_provider.cu) ----
+ * The folded linear model and stage schedule, field for field DeviceRerankLearnedStopConfig
+ * (src/io/bam_vector_provider.cu:65-79). */
+#define TANN_RERANK_STOP_FEATURES 13
+#define TANN_RERANK_STOP_MAX_STAGES 64
+#define TANN_RERANK_STOP_HEAD_PROBE 8 /* ranks of the next window that are looked at (:56) */
+typedef struct TannRerankLearnedStop {
+    uint32_t enabled;
+    uint32_t feature_variant; /* 0 = all 13 features, 1 = the six-feature variant (:59-63) */
+    uint32_t num_stages;
+    uint32_t top_k;
+    uint32_t bootstrap_prefix;
+    uint32_t initial_stage_index;
+    uint32_t stage_prefixes[TANN_RERANK_STOP_MAX_STAGES];
+    float linear_weights[TANN_RERANK_STOP_FEATURES];
+    float bias;
+    float threshold_logit;
+    float budget_log2;
+    float inv_budget_top_n;
+    float inv_top_k;
+} TannRerankLearnedStop;
+
+/* Reads a model file ("key = value" lines: stage_prefixes, feature_means, feature_inv_stds, weights,
+ * feature_mask, bias, threshold_logit, threshold_logit_top_l_<n>, top_k, bootstrap_prefix; 13 features or
+ * the older 12) and folds it for a rerank budget of budget_top_n ranks, as
+ * LoadRerankLearnedStopConfigFromFile does (src/io/bam_vector_provider.cu:125-279). Host only. */
+TannStatus tann_rerank_learned_stop_load(const char* path, uint32_t budget_top_n, uint32_t top_k,
+                                         TannRerankLearnedStop* out);
+
+/*
+ * Exact rerank with the reference's learned stop, stage schedule and stop-prefix replay
+ * (persistent_bam_rerank_kernel_float32_dim, src/io/bam_vector_provider.cu:721-1323, with the vectors
+ * read from the index view instead of the NVMe page cache). Per query a sorted list of the top_k best
+ * (distance, id) is kept; ranks [0, min(top_n, capacity)) are scored window by window: up to
+ * model->bootstrap_prefix, then from stage prefix to stage prefix (plain tiles of params->tile ranks when
+ * the model is NULL or not enabled, and after the last stage). At a stage boundary the 13 features
+ * are taken (:542-596, :976-1019) and the query stops when the logit falls below threshold_logit. With
+ * replay_stop_prefixes the model is not evaluated; query q stops at the first window end >= its
+ * recorded prefix (:1111-1122). params->use_early_stop applies at window ends where no stage is due
+ * (:1123-1135); params->use_bound_filter as in tann_rerank_exact. The next-window features (weights 8
+ * and 9) read the candidates' lower bounds, so a model that uses them needs error_bounds.
+ *   out_dists / out_ids     dev [Q][top_k], sorted, unfilled = (+inf, 0xffffffff);
+ *   out_stop_prefixes       dev [Q] ranks scored when the query stopped (min(top_n, capacity) if it never did);
+ *   out_checkpoint_counts   dev [Q] model evaluations; out_stop_flags dev [Q] 1 = stopped by the model / replay /
+ *                           early stop. All three optional.
+ */
+TannStatus tann_rerank_exact_learned_stop(const TannIndexView* index, const TannRerankParams* params,
+                                          const TannRerankLearnedStop* model /*host or NULL*/,
+                                          const void* candidates /*dev [Q][capacity]*/, uint32_t capacity,
+                                          uint64_t num_queries, const void* queries /*dev [Q][dim]*/,
+                                          uint32_t query_kind, const float* error_bounds /*dev [N] or NULL*/,
+                                          const uint32_t* replay_stop_prefixes /*dev [Q] or NULL*/,
+                                          float* out_dists /*dev*/, uint32_t* out_ids /*dev*/,
+                                          unsigned long long* out_counts /*dev or NULL*/,
+                                          uint32_t* out_stop_prefixes, uint32_t* out_checkpoint_counts,
+                                          uint32_t* out_stop_flags, uint32_t* status, tann_stream_t stream);
+
 /* Copies the first top_k (distance, id) pairs of every sorted list into dense [Q][top_k] arrays
  * (one small D2H copy instead of the reference's per-query host loops,
  * src/search/rerank_exact.cu:1310-1374). */

@@ -212,6 +212,107 @@ def rerank(cand, queries, vector_pages, vec_dtype, *, top_n, top_k, tile=0, vect
     return dists, ids, int(counts[0]), int(counts[1])
 
 
+# ----- learned rerank stop (src/io/bam_vector_provider.cu) -----------------------------------
+
+class RerankStop(C.Structure):
+    """DeviceRerankLearnedStopConfig, src/io/bam_vector_provider.cu:65-79."""
+    _fields_ = [("enabled", C.c_uint32), ("feature_variant", C.c_uint32), ("num_stages", C.c_uint32),
+                ("top_k", C.c_uint32), ("bootstrap_prefix", C.c_uint32), ("initial_stage_index", C.c_uint32),
+                ("stage_prefixes", C.c_uint32 * 64), ("linear_weights", C.c_float * 13), ("bias", C.c_float),
+                ("threshold_logit", C.c_float), ("budget_log2", C.c_float), ("inv_budget_top_n", C.c_float),
+                ("inv_top_k", C.c_float)]
+
+
+def load_rerank_stop_model(path, budget_top_n, top_k):
+    """LoadRerankLearnedStopConfigFromFile, src/io/bam_vector_provider.cu:125-279, in float32 steps."""
+    f32 = np.float32
+    lists, scalars, per_budget = {}, {}, {}
+    with open(path) as fh:
+        for raw in fh:
+            line = raw.strip()
+            if not line or line.startswith("#"):
+                continue
+            if "=" not in line:
+                raise ValueError("Invalid learned-stop config line: " + line)
+            key, value = (t.strip() for t in line.split("=", 1))
+            if key in ("stage_prefixes", "feature_mask"):
+                lists[key] = [int(t) for t in (u.strip() for u in value.split(",")) if t]
+            elif key in ("feature_means", "feature_inv_stds", "weights"):
+                lists[key] = [f32(t) for t in (u.strip() for u in value.split(",")) if t]
+            elif key in ("bias", "threshold_logit"):
+                scalars[key] = f32(value)
+            elif key in ("top_k", "bootstrap_prefix"):
+                scalars[key] = int(value)
+            elif key.startswith("threshold_logit_top_l_") and key[len("threshold_logit_top_l_"):]:
+                per_budget.setdefault(int(key[len("threshold_logit_top_l_"):]), f32(value))
+    means, stds, weights = (lists.get(k, []) for k in ("feature_means", "feature_inv_stds", "weights"))
+    mask = lists.get("feature_mask", [])
+    n = len(weights)
+    if n not in (12, 13) or len(means) != n or len(stds) != n:
+        raise ValueError("learned-stop feature vectors must all have length 13 or 12.")
+    if mask and len(mask) != n:
+        raise ValueError("feature_mask must have length %d." % n)
+    c = RerankStop()
+    if n == 13 and mask == [1, 1, 1, 0, 0, 1, 0, 1, 0, 1, 0, 0, 0]:
+        c.feature_variant = 1
+    c.top_k = scalars.get("top_k", 0) or top_k
+    c.bootstrap_prefix = scalars.get("bootstrap_prefix", 0)
+    c.threshold_logit = per_budget.get(budget_top_n, scalars.get("threshold_logit", f32(0)))
+    c.budget_log2 = f32(np.log2(max(f32(1), f32(budget_top_n)), dtype=f32))
+    c.inv_budget_top_n = f32(0) if budget_top_n == 0 else f32(1) / f32(budget_top_n)
+    c.inv_top_k = f32(0) if c.top_k == 0 else f32(1) / f32(c.top_k)
+    bias = f32(scalars.get("bias", f32(0)))
+    for src in range(n):
+        dst = src + 1 if (n == 12 and src >= 5) else src   # the older single churn ratio is feature 6 now
+        w = weights[src] if (not mask or mask[src] != 0) else f32(0)
+        folded = f32(w * stds[src])
+        c.linear_weights[dst] = folded
+        bias = f32(bias - f32(means[src] * folded))
+    c.bias = bias
+    for prefix in lists.get("stage_prefixes", []):
+        if prefix == 0 or prefix > budget_top_n:
+            continue
+        if c.num_stages >= 64:
+            break
+        c.stage_prefixes[c.num_stages] = prefix
+        c.num_stages += 1
+    while c.initial_stage_index < c.num_stages and c.stage_prefixes[c.initial_stage_index] <= c.bootstrap_prefix:
+        c.initial_stage_index += 1
+    c.enabled = 0 if (c.num_stages == 0 or c.bootstrap_prefix == 0) else 1
+    if c.top_k == 0 or c.top_k > 128:
+        c.enabled = 0
+    return c
+
+
+def rerank_learned(cand, queries, vector_pages, vec_dtype, *, top_n, top_k, tile, vectors_per_page, page_bytes,
+                   vector_bytes, model=None, replay=None, error_bounds=None, use_early_stop=False,
+                   early_stop_min_prefix=0, early_stop_patience_tiles=0):
+    """Persistent rerank with the learned stop. Returns a dict: dists / ids [Q, top_k], stop_prefixes,
+    checkpoint_counts, stop_flags [Q], n_exact, n_filtered."""
+    cand = _c(cand, np.uint32)
+    Q, capacity, _ = cand.shape
+    queries = np.ascontiguousarray(queries)
+    pages = _c(vector_pages, np.uint8)
+    dists = np.empty((Q, top_k), np.float32)
+    ids = np.empty((Q, top_k), np.uint32)
+    counts = np.zeros(2, np.uint64)
+    stop_prefixes = np.zeros(Q, np.uint32)
+    checkpoints = np.zeros(Q, np.uint32)
+    flags = np.zeros(Q, np.uint32)
+    replay_arr = _c(replay, np.uint32) if replay is not None else None
+    lib().orc_rerank_learned(
+        _p(cand), C.c_uint64(Q), C.c_uint32(capacity), C.c_uint32(top_n), C.c_uint32(top_k), C.c_uint32(tile),
+        _p(queries), kind_of(queries), C.c_uint32(queries.shape[1]), _p(pages), KIND[np.dtype(vec_dtype).name],
+        C.c_uint64(vectors_per_page), C.c_uint64(page_bytes), C.c_uint64(vector_bytes),
+        1 if error_bounds is not None else 0,
+        _p(_c(error_bounds, np.float32)) if error_bounds is not None else None,
+        C.byref(model) if model is not None else None, _p(replay_arr) if replay_arr is not None else None,
+        1 if use_early_stop else 0, C.c_uint32(early_stop_min_prefix), C.c_uint32(early_stop_patience_tiles),
+        _p(dists), _p(ids), _p(counts), _p(stop_prefixes), _p(checkpoints), _p(flags))
+    return dict(dists=dists, ids=ids, stop_prefixes=stop_prefixes, checkpoint_counts=checkpoints, stop_flags=flags,
+                n_exact=int(counts[0]), n_filtered=int(counts[1]))
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

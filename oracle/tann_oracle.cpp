@@ -761,6 +761,203 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
     if (counts) { counts[0] += n_exact; counts[1] += n_filtered; }
 }
 
+// Folded learned rerank-stop model, field for field the reference's DeviceRerankLearnedStopConfig
+// (src/io/bam_vector_provider.cu:65-79).
+struct OrcRerankStop {
+    uint32_t enabled, feature_variant, num_stages, top_k, bootstrap_prefix, initial_stage_index;
+    uint32_t stage_prefixes[64];
+    float linear_weights[13];
+    float bias, threshold_logit, budget_log2, inv_budget_top_n, inv_top_k;
+};
+
+// src/io/bam_vector_provider.cu:542-596
+static float OrcStopLogit13(const OrcRerankStop& c, uint32_t processed_prefix, float current_kth, float delta_kth_last,
+                            float delta_kth_prev, float topk_changed_flag, uint32_t entered_topk_count, float topk_spread,
+                            uint32_t next_window_live_count, uint32_t next_window_count, float best_live_lb,
+                            uint32_t window_exact_count, uint32_t window_candidate_count, uint32_t cumulative_exact_count) {
+    const float f1 = (float)processed_prefix * c.inv_budget_top_n;
+    const float f6 = (float)entered_topk_count * c.inv_top_k;
+    const float f8 = next_window_count == 0 ? 0.0f : (float)next_window_live_count / (float)next_window_count;
+    const float f9 = std::isfinite(best_live_lb) ? (best_live_lb - current_kth) : 0.0f;
+    const float inv_window = window_candidate_count == 0 ? 0.0f : 1.0f / (float)window_candidate_count;
+    const float f10 = (float)window_exact_count * inv_window;
+    const float f11 = (float)(window_candidate_count - window_exact_count) * inv_window;
+    const float f12 = processed_prefix == 0 ? 0.0f : (float)cumulative_exact_count / (float)processed_prefix;
+    const float f[13] = {c.budget_log2, f1, current_kth, delta_kth_last, delta_kth_prev, topk_changed_flag, f6,
+                         topk_spread, f8, f9, f10, f11, f12};
+    float logit = c.bias;
+    for (int i = 0; i < 13; ++i) logit = fmaf(f[i], c.linear_weights[i], logit);
+    return logit;
+}
+
+// src/io/bam_vector_provider.cu:598-617: features 0, 1, 2, 5, 7, 9 only
+static float OrcStopLogit6(const OrcRerankStop& c, uint32_t processed_prefix, float current_kth,
+                           float topk_changed_flag, float topk_spread, float best_live_lb) {
+    const float f1 = (float)processed_prefix * c.inv_budget_top_n;
+    const float f9 = std::isfinite(best_live_lb) ? (best_live_lb - current_kth) : 0.0f;
+    float logit = c.bias;
+    logit = fmaf(c.budget_log2, c.linear_weights[0], logit);
+    logit = fmaf(f1, c.linear_weights[1], logit);
+    logit = fmaf(current_kth, c.linear_weights[2], logit);
+    logit = fmaf(topk_changed_flag, c.linear_weights[5], logit);
+    logit = fmaf(topk_spread, c.linear_weights[7], logit);
+    return fmaf(f9, c.linear_weights[9], logit);
+}
+
+static bool PairLess(float ad, uint32_t ai, float bd, uint32_t bi) {   // :525-533
+    if (ad != bd) return ad < bd;
+    return ai < bi;
+}
+
+// Persistent rerank with the learned stop, the stage schedule and stop-prefix replay:
+// src/io/bam_vector_provider.cu:721-1323, one query at a time, in the kernel's own order (window
+// scored, window sorted, ascending insertion into the top_k list with one "entered" count, then
+// the checkpoint / replay / early-stop rule of thread 0). model may be null (plain tiles).
+// replay may be null. use_bound_filter needs error_bounds; the lower bounds of :655-681 are
+// computed where they are read. Outputs: out_dists / out_ids [Q][top_k]; stop_prefixes,
+// checkpoint_counts, stop_flags [Q]; counts[0] += exact, counts[1] += filtered.
+void orc_rerank_learned(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top_n, uint32_t top_k,
+                        uint32_t tile, const void* queries, int query_kind, uint32_t d,
+                        const uint8_t* vector_pages, int vec_kind, uint64_t vectors_per_page,
+                        uint64_t page_bytes, uint64_t vector_bytes, int use_bound_filter,
+                        const float* error_bounds, const OrcRerankStop* model, const uint32_t* replay,
+                        int use_early_stop, uint32_t early_stop_min_prefix, uint32_t early_stop_patience_tiles,
+                        float* out_dists, uint32_t* out_ids, uint64_t* counts, uint32_t* stop_prefixes,
+                        uint32_t* checkpoint_counts, uint32_t* stop_flags) {
+    const Cand* in = static_cast<const Cand*>(cand_in);
+    const float inf = std::numeric_limits<float>::infinity();
+    const uint64_t qbytes = (uint64_t)d * (query_kind == 2 ? 4 : 1);
+    const uint32_t budget = std::min(top_n, capacity);
+    if (tile == 0) tile = budget;
+    OrcRerankStop ls;
+    std::memset(&ls, 0, sizeof(ls));
+    if (model) ls = *model;
+    const bool use_schedule = ls.enabled != 0;                 // :2561-2567
+    const bool evaluate = use_schedule && replay == nullptr;   // :2568-2569
+    uint64_t n_exact = 0, n_filtered = 0;
+    for (uint64_t q = 0; q < Q; ++q) {
+        const uint8_t* qp = static_cast<const uint8_t*>(queries) + q * qbytes;
+        float qnorm = 0.0f;
+        if (use_bound_filter) {
+            double s = 0.0;
+            for (uint32_t i = 0; i < d; ++i) {
+                const double v = (double)LoadScalar(qp, query_kind, i);
+                s += v * v;
+            }
+            qnorm = (float)s;
+        }
+        const auto lower_bound_of_rank = [&](uint32_t r) {
+            const Cand c = in[q * capacity + r];
+            if (c.id == kInvalid) return inf;
+            return LowerBound(c.dist - qnorm, error_bounds[RawId(c.id)]);
+        };
+        std::vector<float> top_d(top_k, inf);
+        std::vector<uint32_t> top_i(top_k, kInvalid);
+        float current_kth = inf, previous_checkpoint_kth = inf, previous_delta = 0.0f;
+        uint32_t exact_count = 0, stable_tiles = 0, stage = ls.initial_stage_index, checkpoints = 0;
+        uint32_t next_prefix = use_schedule ? std::min(budget, ls.bootstrap_prefix) : std::min(budget, tile);
+        uint32_t stop_prefix = budget;
+        bool has_previous = false, stop = false;
+        for (uint32_t rank_begin = 0; rank_begin < budget && !stop;) {
+            const uint32_t rank_end = use_schedule ? next_prefix : std::min(budget, rank_begin + tile);
+            const uint32_t rank_count = rank_end - rank_begin;
+            std::vector<std::pair<float, uint32_t>> window;
+            for (uint32_t r = rank_begin; r < rank_end; ++r) {
+                const Cand c = in[q * capacity + r];
+                if (c.id == kInvalid) continue;
+                const uint32_t id = RawId(c.id);
+                if (use_bound_filter && std::isfinite(current_kth) && lower_bound_of_rank(r) > current_kth) {
+                    ++n_filtered;
+                    continue;
+                }
+                const uint8_t* vp = vector_pages + (id / vectors_per_page) * page_bytes + (id % vectors_per_page) * vector_bytes;
+                window.emplace_back(orc_exact_distance(qp, query_kind, vp, vec_kind, d), id);
+                ++exact_count;
+                ++n_exact;
+            }
+            std::stable_sort(window.begin(), window.end(), [](const auto& a, const auto& b) {
+                return PairLess(a.first, a.second, b.first, b.second);
+            });
+            const float previous_window_kth = top_d[top_k - 1];
+            uint32_t entered = 0;
+            for (const auto& e : window) {   // :619-642
+                if (!PairLess(e.first, e.second, top_d[top_k - 1], top_i[top_k - 1])) continue;
+                uint32_t ins = top_k - 1;
+                while (ins > 0 && PairLess(e.first, e.second, top_d[ins - 1], top_i[ins - 1])) {
+                    top_d[ins] = top_d[ins - 1];
+                    top_i[ins] = top_i[ins - 1];
+                    --ins;
+                }
+                top_d[ins] = e.first;
+                top_i[ins] = e.second;
+                ++entered;
+            }
+            const uint32_t processed = rank_end;
+            current_kth = top_d[top_k - 1];
+            if (evaluate && ls.enabled && std::isfinite(current_kth) && stage < ls.num_stages &&
+                processed >= ls.stage_prefixes[stage]) {
+                const float delta_last = has_previous ? (previous_checkpoint_kth - current_kth) : 0.0f;
+                const float spread = current_kth - top_d[0];
+                const float changed = entered == 0 ? 0.0f : 1.0f;
+                uint32_t next_end = (stage + 1 < ls.num_stages) ? std::min(budget, ls.stage_prefixes[stage + 1])
+                                                                : std::min(budget, rank_end + tile);
+                if (next_end < rank_end) next_end = rank_end;
+                next_end = std::min(next_end, rank_end + 8u);   // head probe, :56,1008-1009
+                uint32_t live = 0;
+                float best_lb = inf;
+                if (ls.linear_weights[8] != 0.0f || ls.linear_weights[9] != 0.0f) {
+                    for (uint32_t r = rank_end; r < next_end; ++r) {
+                        const float lb = lower_bound_of_rank(r);
+                        if (lb <= current_kth) {
+                            ++live;
+                            best_lb = fminf(best_lb, lb);
+                        }
+                    }
+                }
+                const float logit =
+                    ls.feature_variant == 1
+                        ? OrcStopLogit6(ls, processed, current_kth, changed, spread, best_lb)
+                        : OrcStopLogit13(ls, processed, current_kth, delta_last, previous_delta, changed, entered, spread,
+                                         live, next_end - rank_end, best_lb, (uint32_t)window.size(), rank_count,
+                                         exact_count);
+                ++checkpoints;
+                if (logit < ls.threshold_logit) {
+                    stop = true;
+                    stop_prefix = processed;
+                }
+                previous_checkpoint_kth = current_kth;
+                previous_delta = delta_last;
+                has_previous = true;
+                ++stage;
+            } else if (replay != nullptr) {
+                while (stage < ls.num_stages && ls.stage_prefixes[stage] <= processed) ++stage;
+                if (processed >= replay[q]) {
+                    stop = true;
+                    stop_prefix = processed;
+                }
+            } else if (use_early_stop && processed >= early_stop_min_prefix && std::isfinite(current_kth)) {
+                if (current_kth < previous_window_kth) stable_tiles = 0; else ++stable_tiles;
+                if (stable_tiles >= early_stop_patience_tiles) {
+                    stop = true;
+                    stop_prefix = processed;
+                }
+            }
+            if (use_schedule && !stop)
+                next_prefix = stage < ls.num_stages ? std::min(budget, ls.stage_prefixes[stage])
+                                                    : std::min(budget, processed + tile);
+            rank_begin = rank_end;
+        }
+        for (uint32_t i = 0; i < top_k; ++i) {
+            out_dists[q * top_k + i] = top_d[i];
+            out_ids[q * top_k + i] = top_i[i];
+        }
+        if (stop_prefixes) stop_prefixes[q] = stop_prefix;
+        if (checkpoint_counts) checkpoint_counts[q] = checkpoints;
+        if (stop_flags) stop_flags[q] = stop ? 1u : 0u;
+    }
+    if (counts) { counts[0] += n_exact; counts[1] += n_filtered; }
+}
+
 int orc_num_threads() {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -67,6 +67,15 @@ class RerankParams(C.Structure):
                 ("reserved", C.c_uint32)]
 
 
+class RerankLearnedStop(C.Structure):
+    """TannRerankLearnedStop: the folded learned rerank-stop model and its stage schedule."""
+    _fields_ = [("enabled", C.c_uint32), ("feature_variant", C.c_uint32), ("num_stages", C.c_uint32),
+                ("top_k", C.c_uint32), ("bootstrap_prefix", C.c_uint32), ("initial_stage_index", C.c_uint32),
+                ("stage_prefixes", C.c_uint32 * 64), ("linear_weights", C.c_float * 13), ("bias", C.c_float),
+                ("threshold_logit", C.c_float), ("budget_log2", C.c_float), ("inv_budget_top_n", C.c_float),
+                ("inv_top_k", C.c_float)]
+
+
 class RvqModelView(C.Structure):
     _fields_ = [
         ("dim", C.c_uint32), ("num_coarse", C.c_uint32), ("num_fine", C.c_uint32),
@@ -104,6 +113,10 @@ SIGNATURES = {
     "tann_pq2_cross_terms": (_I, [_U32, _U32, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "tann_rerank_exact": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                _VP, _VP, _VP, _VP, _VP, _VP]),
+    "tann_rerank_learned_stop_load": (_I, [C.c_char_p, _U32, _U32, C.POINTER(RerankLearnedStop)]),
+    "tann_rerank_exact_learned_stop": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams),
+                                            C.POINTER(RerankLearnedStop), _VP, _U32, _U64, _VP, _U32, _VP, _VP,
+                                            _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "tann_topk_pack": (_I, [_VP, _VP, _U64, _U32, _U32, _VP, _VP, _VP]),
     "tann_rerank_topk_static": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                      _VP, _VP, _VP, _VP]),

@@ -5,7 +5,12 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <cmath>
+#include <fstream>
+#include <map>
 #include <new>
+#include <string>
+#include <vector>
 
 #include "beam_args.h"
 #include "tann_launch.h"
@@ -304,6 +309,170 @@ TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams*
     if (st != TANN_OK) return st;
     TANN_CUDA(tann::LaunchRerank(*index, *params, candidates, capacity, num_queries, queries, query_kind,
                                  error_bounds, out_dists, out_ids, out_counts, (cudaStream_t)stream));
+    return TANN_OK;
+}
+
+// ---- learned rerank stop -----------------------------------------------------------------------
+
+extern "C++" {
+namespace {
+
+std::string TrimmedCopy(const std::string& text) {
+    size_t a = 0, b = text.size();
+    while (a < b && isspace((unsigned char)text[a])) ++a;
+    while (b > a && isspace((unsigned char)text[b - 1])) --b;
+    return text.substr(a, b - a);
+}
+
+// Comma-separated values, blanks around tokens and empty tokens dropped.
+template <typename T, typename Parse>
+bool ParseList(const std::string& text, Parse parse, std::vector<T>* out) {
+    out->clear();
+    size_t start = 0;
+    while (start <= text.size()) {
+        size_t comma = text.find(',', start);
+        if (comma == std::string::npos) comma = text.size();
+        const std::string token = TrimmedCopy(text.substr(start, comma - start));
+        if (!token.empty()) {
+            try {
+                out->push_back(parse(token));
+            } catch (...) {
+                return false;
+            }
+        }
+        start = comma + 1;
+    }
+    return true;
+}
+
+}  // namespace
+}  // extern "C++"
+
+TannStatus tann_rerank_learned_stop_load(const char* path, uint32_t budget_top_n, uint32_t top_k,
+                                         TannRerankLearnedStop* out) {
+    const char* ctx = "LoadRerankLearnedStopConfigFromFile";
+    if (!path || !out) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: null pointer.", ctx);
+    std::ifstream in(path);
+    if (!in.is_open()) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: Failed to open %s", ctx, path);
+    std::vector<uint32_t> stages, mask;
+    std::vector<float> means, inv_stds, weights;
+    std::map<uint32_t, float> threshold_of_budget;
+    uint32_t file_top_k = 0, bootstrap = 0;
+    float bias = 0.0f, threshold = 0.0f;
+    const auto to_u32 = [](const std::string& t) { return (uint32_t)std::stoul(t); };
+    const auto to_f32 = [](const std::string& t) { return std::stof(t); };
+    const std::string per_budget_key = "threshold_logit_top_l_";
+    std::string raw;
+    while (std::getline(in, raw)) {
+        const std::string line = TrimmedCopy(raw);
+        if (line.empty() || line[0] == '#') continue;
+        const size_t eq = line.find('=');
+        if (eq == std::string::npos)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: Invalid learned-stop config line: %s", ctx, line.c_str());
+        const std::string key = TrimmedCopy(line.substr(0, eq)), value = TrimmedCopy(line.substr(eq + 1));
+        bool ok = true;
+        try {
+            if (key == "stage_prefixes") ok = ParseList(value, to_u32, &stages);
+            else if (key == "feature_means") ok = ParseList(value, to_f32, &means);
+            else if (key == "feature_inv_stds") ok = ParseList(value, to_f32, &inv_stds);
+            else if (key == "weights") ok = ParseList(value, to_f32, &weights);
+            else if (key == "feature_mask") ok = ParseList(value, to_u32, &mask);
+            else if (key == "bias") bias = std::stof(value);
+            else if (key == "threshold_logit") threshold = std::stof(value);
+            else if (key == "top_k") file_top_k = (uint32_t)std::stoul(value);
+            else if (key == "bootstrap_prefix") bootstrap = (uint32_t)std::stoul(value);
+            else if (key.compare(0, per_budget_key.size(), per_budget_key) == 0 && key.size() > per_budget_key.size())
+                threshold_of_budget.emplace((uint32_t)std::stoul(key.substr(per_budget_key.size())), std::stof(value));
+        } catch (...) {
+            ok = false;
+        }
+        if (!ok) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: Invalid learned-stop config value: %s", ctx, line.c_str());
+    }
+    const size_t kNow = TANN_RERANK_STOP_FEATURES, kOlder = 12;
+    const bool older = means.size() == kOlder && inv_stds.size() == kOlder && weights.size() == kOlder;
+    const bool now = means.size() == kNow && inv_stds.size() == kNow && weights.size() == kNow;
+    if (!older && !now)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: learned-stop feature vectors must all have length 13 or 12.", ctx);
+    if (!mask.empty() && mask.size() != (older ? kOlder : kNow))
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: feature_mask must have length %zu.", ctx, older ? kOlder : kNow);
+
+    TannRerankLearnedStop c;
+    memset(&c, 0, sizeof(c));
+    static const uint32_t kSixFeatureMask[TANN_RERANK_STOP_FEATURES] = {1, 1, 1, 0, 0, 1, 0, 1, 0, 1, 0, 0, 0};
+    if (now && mask.size() == kNow && memcmp(mask.data(), kSixFeatureMask, sizeof(kSixFeatureMask)) == 0)
+        c.feature_variant = 1;
+    c.top_k = file_top_k != 0 ? file_top_k : top_k;
+    c.bootstrap_prefix = bootstrap;
+    const auto it = threshold_of_budget.find(budget_top_n);
+    c.threshold_logit = it != threshold_of_budget.end() ? it->second : threshold;
+    c.budget_log2 = std::log2(std::max(1.0f, (float)budget_top_n));
+    c.inv_budget_top_n = budget_top_n == 0 ? 0.0f : 1.0f / (float)budget_top_n;
+    c.inv_top_k = c.top_k == 0 ? 0.0f : 1.0f / (float)c.top_k;
+    // Standardisation folded into the weights: w' = w / std, bias' = bias - sum(mean * w').
+    // The older 12-feature layout has one top-k churn ratio where the kernel has a flag (5) and a ratio (6).
+    float folded_bias = bias;
+    for (size_t src = 0; src < weights.size(); ++src) {
+        const size_t dst = (older && src >= 5) ? src + 1 : src;
+        const float w = (mask.empty() || mask[src] != 0u) ? weights[src] : 0.0f;
+        c.linear_weights[dst] = w * inv_stds[src];
+        folded_bias -= means[src] * c.linear_weights[dst];
+    }
+    c.bias = folded_bias;
+    for (uint32_t prefix : stages) {
+        if (prefix == 0 || prefix > budget_top_n) continue;
+        if (c.num_stages >= TANN_RERANK_STOP_MAX_STAGES) break;
+        c.stage_prefixes[c.num_stages++] = prefix;
+    }
+    while (c.initial_stage_index < c.num_stages && c.stage_prefixes[c.initial_stage_index] <= c.bootstrap_prefix)
+        ++c.initial_stage_index;
+    c.enabled = (c.num_stages == 0 || c.bootstrap_prefix == 0) ? 0u : 1u;
+    if (c.top_k == 0 || c.top_k > 128) c.enabled = 0;
+    *out = c;
+    return TANN_OK;
+}
+
+TannStatus tann_rerank_exact_learned_stop(const TannIndexView* index, const TannRerankParams* params,
+                                          const TannRerankLearnedStop* model, const void* candidates,
+                                          uint32_t capacity, uint64_t num_queries, const void* queries,
+                                          uint32_t query_kind, const float* error_bounds,
+                                          const uint32_t* replay_stop_prefixes, float* out_dists, uint32_t* out_ids,
+                                          unsigned long long* out_counts, uint32_t* out_stop_prefixes,
+                                          uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, uint32_t* status,
+                                          tann_stream_t stream) {
+    (void)status;
+    const char* ctx = "tann_rerank_exact_learned_stop";
+    if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: null index or params.", ctx);
+    if (num_queries == 0 || params->top_n == 0 || capacity == 0) return TANN_OK;
+    if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: null pointer.", ctx);
+    if (params->top_k == 0 || params->top_k > 128 || params->top_k > params->top_n)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: Persistent rerank requires 1 <= top_k <= min(top_n, 128).", ctx);
+    TannStatus st = CheckRerank(index, params, error_bounds);
+    if (st != TANN_OK) return st;
+    TannRerankLearnedStop m;
+    memset(&m, 0, sizeof(m));
+    if (model) m = *model;
+    const bool use_schedule = m.enabled != 0;
+    if (use_schedule) {
+        if (m.num_stages > TANN_RERANK_STOP_MAX_STAGES || m.initial_stage_index > m.num_stages)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: bad stage count in the model.", ctx);
+        // The kernel walks the stages in order; a prefix that does not grow would give an empty or
+        // negative window (the reference's kernel reads out of bounds there).
+        uint32_t last = m.bootstrap_prefix;
+        if (last == 0) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: an enabled model needs bootstrap_prefix >= 1.", ctx);
+        for (uint32_t i = m.initial_stage_index; i < m.num_stages; ++i) {
+            if (m.stage_prefixes[i] <= last)
+                return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: stage prefixes must increase and exceed bootstrap_prefix.", ctx);
+            last = m.stage_prefixes[i];
+        }
+        if ((m.linear_weights[8] != 0.0f || m.linear_weights[9] != 0.0f) && !params->use_bound_filter)
+            return Fail(TANN_ERR_INVALID_ARGUMENT,
+                        "%s: a model with next-window features needs the PQ2 bound filter (lower bounds).", ctx);
+    }
+    TANN_CUDA(tann::LaunchRerankLearned(*index, *params, m, use_schedule, use_schedule && replay_stop_prefixes == nullptr,
+                                        candidates, capacity, num_queries, queries, query_kind, error_bounds,
+                                        replay_stop_prefixes, out_dists, out_ids, out_counts, out_stop_prefixes,
+                                        out_checkpoint_counts, out_stop_flags, (cudaStream_t)stream));
     return TANN_OK;
 }
 

@@ -193,6 +193,93 @@ __device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const 
     }
 }
 
+// How a block scores its ranks; the same for every tile of a query.
+struct ScoreMode {
+    bool int_path;      // uint8 rows and uint8 queries: integer arithmetic
+    bool octet_int;     // ... with rows on 16-byte boundaries and dim a multiple of 16
+    bool octet_f32;     // float rows, float queries, rows on 16-byte boundaries
+    bool octet_u8f32;   // uint8 rows, float queries
+    uint32_t qkind;
+};
+
+// Exact distances of ranks [rb, end): keys[r] holds the address of rank r's vector (or the invalid
+// key) on entry and its (distance, id) sort key on return. Called by all threads of the block.
+__device__ __forceinline__ void ScoreRanks(const TannIndexView& ix, const ScoreMode& m, unsigned long long* keys,
+                                           const uint32_t* rank_ids, const uint8_t* qrow, uint32_t rb, uint32_t end) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t dim = ix.dim, rc = end - rb, qkind = m.qkind;
+    const bool int_path = m.int_path, octet_int = m.octet_int, octet_f32 = m.octet_f32, octet_u8f32 = m.octet_u8f32;
+    if (octet_int) {
+        if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+    } else if (octet_f32) {
+        if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksF32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+    } else if (octet_u8f32) {
+        if (rc >= 64) OctetRanksU8F32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksU8F32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+    } else {
+        // A warp scores kGroup candidates per step: all their row loads are issued before any
+        // reduction, so several random reads are in flight per lane.
+        constexpr uint32_t kGroup = 4;
+        for (uint32_t r0 = rb + warp * kGroup; r0 < end; r0 += (kRerankThreads / 32) * kGroup) {
+            const uint8_t* vptr[kGroup];
+            bool act[kGroup];
+#pragma unroll
+            for (uint32_t g = 0; g < kGroup; ++g) {
+                const unsigned long long slot = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
+                act[g] = slot != kInvalidKey64;
+                vptr[g] = reinterpret_cast<const uint8_t*>(slot);
+            }
+            float dist[kGroup];
+            if (int_path) {
+                uint32_t acc[kGroup];
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0;
+                const uint32_t* q4 = reinterpret_cast<const uint32_t*>(qrow);
+                for (uint32_t i = lane; i < dim / 4; i += 32) {
+                    uint32_t w[kGroup];
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g)
+                        w[g] = act[g] ? __ldg(reinterpret_cast<const uint32_t*>(vptr[g]) + i) : 0u;
+                    const uint32_t qw = q4[i];
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) acc[g] = SqDiffBytes(w[g], qw, acc[g]);
+                }
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g) {
+#pragma unroll
+                    for (int off = 16; off >= 1; off >>= 1) acc[g] += __shfl_xor_sync(kFull, acc[g], off);
+                    dist[g] = static_cast<float>(acc[g]);
+                }
+            } else {
+                float acc[kGroup];
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0.0f;
+                for (uint32_t i = lane; i < dim; i += 32) {
+                    float v[kGroup];
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g)
+                        v[g] = act[g] ? LoadAsFloat<float>(vptr[g], ix.vector_kind, i) : 0.0f;
+                    const float qv = LoadAsFloat<float>(qrow, qkind, i);
+#pragma unroll
+                    for (uint32_t g = 0; g < kGroup; ++g) {
+                        const float diff = v[g] - qv;
+                        acc[g] = fmaf(diff, diff, acc[g]);
+                    }
+                }
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g) dist[g] = WarpTreeSum(acc[g]);
+            }
+            if (lane == 0) {
+#pragma unroll
+                for (uint32_t g = 0; g < kGroup; ++g)
+                    if (act[g]) keys[r0 + g] = KeyOf(dist[g], rank_ids[r0 + g]);
+            }
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kRerankThreads)
 rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, const Cand* __restrict__ cand,
               uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
@@ -228,6 +315,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                            qkind == TANN_KIND_FLOAT32 && (dim % 4 == 0);
     const bool octet_u8f32 = !int_path && ix.vector_kind == TANN_KIND_UINT8 && qkind == TANN_KIND_FLOAT32 &&
                              (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0) && (dim % 4 == 0);
+    const ScoreMode mode{int_path, octet_int, octet_f32, octet_u8f32, qkind};
     unsigned long long tot_exact = 0, tot_filtered = 0;
 
     for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
@@ -286,76 +374,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
             if (lane == 0 && n_flt) atomicAdd(&s_filtered, n_flt);
             __syncthreads();
             // ---- distances --------------------------------------------------------------------
-            const uint32_t end = rb + rc;
-            if (octet_int) {
-                if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-                else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-            } else if (octet_f32) {
-                if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-                else OctetRanksF32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-            } else if (octet_u8f32) {
-                if (rc >= 64) OctetRanksU8F32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-                else OctetRanksU8F32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-            } else {
-                // A warp scores kGroup candidates per step: all their row loads are issued before any
-                // reduction, so several random reads are in flight per lane.
-                constexpr uint32_t kGroup = 4;
-                for (uint32_t r0 = rb + warp * kGroup; r0 < end; r0 += (kRerankThreads / 32) * kGroup) {
-                    const uint8_t* vptr[kGroup];
-                    bool act[kGroup];
-#pragma unroll
-                    for (uint32_t g = 0; g < kGroup; ++g) {
-                        const unsigned long long slot = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
-                        act[g] = slot != kInvalidKey64;
-                        vptr[g] = reinterpret_cast<const uint8_t*>(slot);
-                    }
-                    float dist[kGroup];
-                    if (int_path) {
-                        uint32_t acc[kGroup];
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0;
-                        const uint32_t* q4 = reinterpret_cast<const uint32_t*>(qrow);
-                        for (uint32_t i = lane; i < dim / 4; i += 32) {
-                            uint32_t w[kGroup];
-#pragma unroll
-                            for (uint32_t g = 0; g < kGroup; ++g)
-                                w[g] = act[g] ? __ldg(reinterpret_cast<const uint32_t*>(vptr[g]) + i) : 0u;
-                            const uint32_t qw = q4[i];
-#pragma unroll
-                            for (uint32_t g = 0; g < kGroup; ++g) acc[g] = SqDiffBytes(w[g], qw, acc[g]);
-                        }
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g) {
-#pragma unroll
-                            for (int off = 16; off >= 1; off >>= 1) acc[g] += __shfl_xor_sync(kFull, acc[g], off);
-                            dist[g] = static_cast<float>(acc[g]);
-                        }
-                    } else {
-                        float acc[kGroup];
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g) acc[g] = 0.0f;
-                        for (uint32_t i = lane; i < dim; i += 32) {
-                            float v[kGroup];
-#pragma unroll
-                            for (uint32_t g = 0; g < kGroup; ++g)
-                                v[g] = act[g] ? LoadAsFloat<float>(vptr[g], ix.vector_kind, i) : 0.0f;
-                            const float qv = LoadAsFloat<float>(qrow, qkind, i);
-#pragma unroll
-                            for (uint32_t g = 0; g < kGroup; ++g) {
-                                const float diff = v[g] - qv;
-                                acc[g] = fmaf(diff, diff, acc[g]);
-                            }
-                        }
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g) dist[g] = WarpTreeSum(acc[g]);
-                    }
-                    if (lane == 0) {
-#pragma unroll
-                        for (uint32_t g = 0; g < kGroup; ++g)
-                            if (act[g]) keys[r0 + g] = KeyOf(dist[g], rank_ids[r0 + g]);
-                    }
-                }
-            }
+            ScoreRanks(ix, mode, keys, rank_ids, qrow, rb, rb + rc);
             __syncthreads();
             if (track_kth) {
                 if (tid == 0) {
@@ -448,6 +467,258 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
     }
 }
 
+// ---- rerank with the learned stop ------------------------------------------------------------
+// The reference's persistent rerank (src/io/bam_vector_provider.cu:721-1323) with the vectors read
+// from the index view: per query a sorted list of the top_k best (distance, id); ranks are scored
+// window by window (bootstrap prefix, then stage prefix to stage prefix, then plain tiles); at a stage
+// boundary thread 0 takes the features and evaluates the folded linear model. The reference sorts a
+// window and inserts it in ascending order into the list with one thread; here every thread places
+// one window entry and one list entry by counting (a parallel merge). An entry enters exactly when
+// fewer than top_k entries of (list + earlier window entries) are <= it, which is the reference's
+// test against the list's last element at its turn, so the list and the entered count are the same.
+
+__device__ __forceinline__ float KeyDist(unsigned long long k) { return FromOrderedBits((uint32_t)(k >> 32)); }
+
+// src/io/bam_vector_provider.cu:542-596 (all 13 features) and :598-617 (six-feature variant)
+__device__ __forceinline__ float RerankStopLogit(const TannRerankLearnedStop& c, uint32_t processed_prefix,
+                                                 float current_kth, float delta_kth_last, float delta_kth_prev,
+                                                 float topk_changed_flag, uint32_t entered_topk_count, float topk_spread,
+                                                 uint32_t next_live, uint32_t next_count, float best_live_lb,
+                                                 uint32_t window_exact, uint32_t window_count, uint32_t cumulative_exact) {
+    const float prefix_frac = static_cast<float>(processed_prefix) * c.inv_budget_top_n;
+    const float lb_gap = isfinite(best_live_lb) ? (best_live_lb - current_kth) : 0.0f;
+    float logit = c.bias;
+    logit = fmaf(c.budget_log2, c.linear_weights[0], logit);
+    logit = fmaf(prefix_frac, c.linear_weights[1], logit);
+    logit = fmaf(current_kth, c.linear_weights[2], logit);
+    if (c.feature_variant == 1u) {
+        logit = fmaf(topk_changed_flag, c.linear_weights[5], logit);
+        logit = fmaf(topk_spread, c.linear_weights[7], logit);
+        return fmaf(lb_gap, c.linear_weights[9], logit);
+    }
+    const float entered_ratio = static_cast<float>(entered_topk_count) * c.inv_top_k;
+    const float live_ratio = next_count == 0u ? 0.0f : static_cast<float>(next_live) / static_cast<float>(next_count);
+    const float inv_window = window_count == 0u ? 0.0f : 1.0f / static_cast<float>(window_count);
+    const float exact_ratio = static_cast<float>(window_exact) * inv_window;
+    const float filtered_ratio = static_cast<float>(window_count - window_exact) * inv_window;
+    const float exact_frac =
+        processed_prefix == 0u ? 0.0f : static_cast<float>(cumulative_exact) / static_cast<float>(processed_prefix);
+    logit = fmaf(delta_kth_last, c.linear_weights[3], logit);
+    logit = fmaf(delta_kth_prev, c.linear_weights[4], logit);
+    logit = fmaf(topk_changed_flag, c.linear_weights[5], logit);
+    logit = fmaf(entered_ratio, c.linear_weights[6], logit);
+    logit = fmaf(topk_spread, c.linear_weights[7], logit);
+    logit = fmaf(live_ratio, c.linear_weights[8], logit);
+    logit = fmaf(lb_gap, c.linear_weights[9], logit);
+    logit = fmaf(exact_ratio, c.linear_weights[10], logit);
+    logit = fmaf(filtered_ratio, c.linear_weights[11], logit);
+    return fmaf(exact_frac, c.linear_weights[12], logit);
+}
+
+__global__ void __launch_bounds__(kRerankThreads)
+rerank_learned_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p,
+                      const __grid_constant__ TannRerankLearnedStop ls, uint32_t use_schedule, uint32_t evaluate,
+                      const Cand* __restrict__ cand, uint32_t capacity, uint64_t Q, const void* __restrict__ queries,
+                      uint32_t qkind, const float* __restrict__ error_bounds, const uint32_t* __restrict__ replay,
+                      uint32_t padded, float* __restrict__ out_dists, uint32_t* __restrict__ out_ids,
+                      unsigned long long* __restrict__ out_counts, uint32_t* __restrict__ out_stop_prefixes,
+                      uint32_t* __restrict__ out_checkpoints, uint32_t* __restrict__ out_stop_flags) {
+    extern __shared__ __align__(16) unsigned char rr_smem[];
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(rr_smem);   // [padded]
+    uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
+    uint8_t* qrow = rr_smem + (((size_t)padded * 12 + 15) & ~(size_t)15);
+    __shared__ unsigned long long s_top[2][kRerankThreads];   // the sorted top_k list, double-buffered
+    __shared__ float s_kth, s_qnorm, s_prev_ckpt_kth, s_prev_delta;
+    __shared__ unsigned int s_exact, s_filtered, s_entered, s_stable, s_stop, s_stage, s_next, s_ckpt, s_stop_prefix,
+        s_has_prev;
+    const uint32_t tid = threadIdx.x, lane = tid & 31;
+    const uint32_t dim = ix.dim, k = p.top_k;
+    const uint32_t budget = min(p.top_n, capacity);
+    const uint32_t tile = p.tile == 0 ? budget : p.tile;
+    const float kInf = __int_as_float(0x7f800000);
+    ScoreMode mode;
+    mode.qkind = qkind;
+    mode.int_path = qkind == TANN_KIND_UINT8 && ix.vector_kind == TANN_KIND_UINT8 && (dim % 4 == 0) && dim <= 256 &&
+                    (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0);
+    const bool rows16 = (ix.vector_bytes % 16 == 0) && (ix.page_bytes % 16 == 0);
+    mode.octet_int = mode.int_path && rows16 && (dim % 16 == 0);
+    mode.octet_f32 = !mode.int_path && rows16 && ix.vector_kind == TANN_KIND_FLOAT32 && qkind == TANN_KIND_FLOAT32 &&
+                     (dim % 4 == 0);
+    mode.octet_u8f32 = !mode.int_path && ix.vector_kind == TANN_KIND_UINT8 && qkind == TANN_KIND_FLOAT32 &&
+                       (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0) && (dim % 4 == 0);
+    const uint32_t qbytes = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
+    unsigned long long tot_exact = 0, tot_filtered = 0;
+
+    for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
+        const uint8_t* qsrc = static_cast<const uint8_t*>(queries) + q * qbytes;
+        for (uint32_t i = tid; i < qbytes; i += kRerankThreads) qrow[i] = qsrc[i];
+        s_top[0][tid] = kInvalidKey64;
+        if (tid == 0) {
+            s_kth = kInf;
+            s_exact = 0; s_filtered = 0; s_entered = 0; s_stable = 0; s_stop = 0;
+            s_stage = ls.initial_stage_index;
+            s_next = use_schedule ? min(budget, ls.bootstrap_prefix) : min(budget, tile);
+            s_ckpt = 0; s_stop_prefix = budget; s_has_prev = 0;
+            s_prev_ckpt_kth = kInf; s_prev_delta = 0.0f;
+        }
+        __syncthreads();
+        if (p.use_bound_filter && tid == 0) {
+            double sum = 0.0;
+            for (uint32_t i = 0; i < dim; ++i) {
+                const double v = (double)LoadAsFloat<float>(qrow, qkind, i);
+                sum += v * v;
+            }
+            s_qnorm = (float)sum;
+        }
+        __syncthreads();
+        uint32_t cur = 0, exact_before = 0;
+        for (uint32_t rb = 0; rb < budget;) {
+            if (s_stop) break;
+            const uint32_t re = use_schedule ? s_next : min(budget, rb + tile);
+            const uint32_t rc = re - rb;
+            const float threshold = s_kth;
+            // ---- one thread per rank: candidate record, bound filter, vector address ----------
+            uint32_t n_act = 0, n_flt = 0;
+            for (uint32_t r = rb + tid; r < re; r += kRerankThreads) {
+                unsigned long long slot = kInvalidKey64;
+                const Cand c = cand[q * capacity + r];
+                const uint32_t id = c.id & kRawMask;
+                if (c.id != kInvalid && id < ix.num_nodes) {
+                    bool keep = true;
+                    if (p.use_bound_filter && isfinite(threshold))
+                        keep = !(LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id)) > threshold);
+                    if (keep) {
+                        slot = reinterpret_cast<unsigned long long>(VectorPtr(ix, id));
+                        rank_ids[r] = id;
+                        ++n_act;
+                    } else {
+                        ++n_flt;
+                    }
+                }
+                keys[r] = slot;
+            }
+            n_act = __reduce_add_sync(kFull, n_act);
+            n_flt = __reduce_add_sync(kFull, n_flt);
+            if (lane == 0 && n_act) atomicAdd(&s_exact, n_act);
+            if (lane == 0 && n_flt) atomicAdd(&s_filtered, n_flt);
+            s_top[cur ^ 1][tid] = kInvalidKey64;
+            __syncthreads();
+            ScoreRanks(ix, mode, keys, rank_ids, qrow, rb, re);
+            __syncthreads();
+            // ---- merge the window into the top_k list (:945-965) ---------------------------------
+            {
+                const unsigned long long* old_list = s_top[cur];
+                unsigned long long* new_list = s_top[cur ^ 1];
+                uint32_t entered = 0;
+                for (uint32_t t = tid; t < rc; t += kRerankThreads) {
+                    const unsigned long long e = keys[rb + t];
+                    if (e == kInvalidKey64) continue;
+                    uint32_t cnt = 0;
+                    for (uint32_t u = 0; u < rc; ++u) {
+                        const unsigned long long x = keys[rb + u];
+                        cnt += (x < e || (x == e && u < t)) ? 1u : 0u;
+                    }
+                    for (uint32_t j = 0; j < k; ++j) cnt += old_list[j] <= e ? 1u : 0u;
+                    if (cnt < k) {
+                        new_list[cnt] = e;
+                        ++entered;
+                    }
+                }
+                if (tid < k) {
+                    const unsigned long long x = old_list[tid];
+                    if (x != kInvalidKey64) {
+                        uint32_t pos = tid;
+                        for (uint32_t u = 0; u < rc; ++u) pos += keys[rb + u] < x ? 1u : 0u;
+                        if (pos < k) new_list[pos] = x;
+                    }
+                }
+                entered = __reduce_add_sync(kFull, entered);
+                if (lane == 0 && entered) atomicAdd(&s_entered, entered);
+            }
+            __syncthreads();
+            cur ^= 1;
+            if (tid == 0) {
+                const unsigned long long* list = s_top[cur];
+                const float previous_window_kth = KeyDist(s_top[cur ^ 1][k - 1]);
+                const uint32_t processed = re;
+                const float kth = KeyDist(list[k - 1]);
+                const uint32_t entered = s_entered;
+                const uint32_t window_exact = s_exact - exact_before;
+                exact_before = s_exact;
+                s_entered = 0;
+                s_kth = kth;
+                uint32_t stage = s_stage;
+                uint32_t stop = 0;
+                if (evaluate && ls.enabled != 0u && isfinite(kth) && stage < ls.num_stages &&
+                    processed >= ls.stage_prefixes[stage]) {   // :981-1110, :1213-1276
+                    const float delta_last = s_has_prev ? (s_prev_ckpt_kth - kth) : 0.0f;
+                    const float spread = kth - KeyDist(list[0]);
+                    uint32_t nwe = (stage + 1u < ls.num_stages) ? min(budget, ls.stage_prefixes[stage + 1u])
+                                                                : min(budget, re + tile);
+                    if (nwe < re) nwe = re;
+                    nwe = min(nwe, re + (uint32_t)TANN_RERANK_STOP_HEAD_PROBE);
+                    uint32_t live = 0;
+                    float best_lb = kInf;
+                    if (ls.linear_weights[8] != 0.0f || ls.linear_weights[9] != 0.0f) {
+                        for (uint32_t r = re; r < nwe; ++r) {
+                            const Cand c = cand[q * capacity + r];
+                            const uint32_t id = c.id & kRawMask;
+                            float lb = kInf;
+                            if (c.id != kInvalid && id < ix.num_nodes)
+                                lb = LowerBoundSq(c.dist - s_qnorm, __ldg(error_bounds + id));
+                            if (lb <= kth) {
+                                ++live;
+                                best_lb = fminf(best_lb, lb);
+                            }
+                        }
+                    }
+                    const float logit = RerankStopLogit(ls, processed, kth, delta_last, s_prev_delta,
+                                                        entered == 0u ? 0.0f : 1.0f, entered, spread, live, nwe - re,
+                                                        best_lb, window_exact, rc, s_exact);
+                    ++s_ckpt;
+                    if (logit < ls.threshold_logit) stop = 1;
+                    s_prev_ckpt_kth = kth;
+                    s_prev_delta = delta_last;
+                    s_has_prev = 1;
+                    ++stage;
+                } else if (replay != nullptr) {   // :1111-1122
+                    while (stage < ls.num_stages && ls.stage_prefixes[stage] <= processed) ++stage;
+                    if (processed >= replay[q]) stop = 1;
+                } else if (p.use_early_stop && processed >= p.early_stop_min_prefix && isfinite(kth)) {   // :1123-1135
+                    if (kth < previous_window_kth) s_stable = 0; else ++s_stable;
+                    if (s_stable >= p.early_stop_patience_tiles) stop = 1;
+                }
+                s_stage = stage;
+                if (stop) {
+                    s_stop = 1;
+                    s_stop_prefix = processed;
+                } else if (use_schedule) {
+                    s_next = stage < ls.num_stages ? min(budget, ls.stage_prefixes[stage]) : min(budget, processed + tile);
+                }
+            }
+            __syncthreads();
+            rb = re;
+        }
+        if (tid < k) {
+            const unsigned long long key = s_top[cur][tid];
+            out_dists[q * k + tid] = KeyDist(key);
+            out_ids[q * k + tid] = (uint32_t)key;
+        }
+        if (tid == 0) {
+            tot_exact += s_exact;
+            tot_filtered += s_filtered;
+            if (out_stop_prefixes != nullptr) out_stop_prefixes[q] = s_stop_prefix;
+            if (out_checkpoints != nullptr) out_checkpoints[q] = s_ckpt;
+            if (out_stop_flags != nullptr) out_stop_flags[q] = s_stop;
+        }
+        __syncthreads();
+    }
+    if (tid == 0 && out_counts != nullptr) {
+        if (tot_exact) atomicAdd(out_counts, tot_exact);
+        if (tot_filtered) atomicAdd(out_counts + 1, tot_filtered);
+    }
+}
+
 __global__ void topk_pack_kernel(const float* __restrict__ dists, const uint32_t* __restrict__ ids,
                                  uint64_t Q, uint32_t top_n, uint32_t top_k,
                                  float* __restrict__ out_dists, uint32_t* __restrict__ out_ids) {
@@ -481,6 +752,31 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     rerank_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, static_cast<const Cand*>(cand), capacity, Q, queries, query_kind, error_bounds, padded,
         out_dists, out_ids, out_counts, queries_u8, not_u8_flag, final_ranks);
+    return cudaGetLastError();
+}
+
+cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams& p, const TannRerankLearnedStop& model,
+                                bool use_schedule, bool evaluate, const void* cand, uint32_t capacity, uint64_t Q,
+                                const void* queries, uint32_t query_kind, const float* error_bounds,
+                                const uint32_t* replay_stop_prefixes, float* out_dists, uint32_t* out_ids,
+                                unsigned long long* out_counts, uint32_t* out_stop_prefixes,
+                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream) {
+    if (Q == 0 || p.top_n == 0 || capacity == 0) return cudaSuccess;
+    const uint32_t budget = p.top_n < capacity ? p.top_n : capacity;
+    uint32_t padded = 1;
+    while (padded < budget) padded <<= 1;
+    const size_t qbytes = (size_t)ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
+    const size_t smem = (((size_t)padded * 12 + 15) & ~(size_t)15) + ((qbytes + 15) & ~(size_t)15);
+    if (smem > 40 * 1024) {   // the kernel also has 2 KB of static shared memory
+        cudaError_t e = cudaFuncSetAttribute(rerank_learned_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    const uint64_t cap = (uint64_t)SmCount() * 8;
+    rerank_learned_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
+        ix, p, model, use_schedule ? 1u : 0u, evaluate ? 1u : 0u, static_cast<const Cand*>(cand), capacity, Q, queries,
+        query_kind, error_bounds, replay_stop_prefixes, padded, out_dists, out_ids, out_counts, out_stop_prefixes,
+        out_checkpoint_counts, out_stop_flags);
     return cudaGetLastError();
 }
 

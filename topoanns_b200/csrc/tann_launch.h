@@ -50,6 +50,13 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
                          const uint8_t* queries_u8 = nullptr, const uint32_t* not_u8_flag = nullptr,
                          uint32_t final_ranks = 0 /* > 0: only the first final_ranks (<= 32) entries of every
                                                      output list are produced (the smallest, in order) */);
+// Rerank with the learned stop / stage schedule / stop-prefix replay; out lists are [Q][top_k].
+cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams& p, const TannRerankLearnedStop& model,
+                                bool use_schedule, bool evaluate, const void* cand, uint32_t capacity, uint64_t Q,
+                                const void* queries, uint32_t query_kind, const float* error_bounds,
+                                const uint32_t* replay_stop_prefixes, float* out_dists, uint32_t* out_ids,
+                                unsigned long long* out_counts, uint32_t* out_stop_prefixes,
+                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream);
 cudaError_t LaunchF32ToU8Checked(const float* src, uint64_t n, uint8_t* dst, uint32_t* not_u8_flag,
                                  cudaStream_t stream);
 cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, uint32_t top_n,

@@ -9,6 +9,8 @@
 #include <cstring>
 #include <fstream>
 #include <map>
+#include <memory>
+#include <mutex>
 #include <sstream>
 #include <unordered_set>
 
@@ -339,6 +341,117 @@ DeviceRerank RunRerankKernel(const SearchResources& resources, const TannIndexVi
     return out;
 }
 
+// ---- learned rerank stop: stop-prefix traces ------------------------------------------------------------------
+// File of records {u32 magic "RSP1", u32 budget_top_n, u32 num_queries, u32 prefix[num_queries]}, one per
+// batch (src/io/rerank_stop_prefix_trace.hpp:16-88). A process truncates a record file the first time it
+// writes to it and appends afterwards; a replay file is read record by record in batch order.
+constexpr std::uint32_t kStopPrefixTraceMagic = 0x52535031u;
+std::mutex g_trace_mutex;
+
+void AppendStopPrefixTrace(const std::string& path, std::size_t budget_top_n, const std::vector<std::uint32_t>& prefixes) {
+    static std::map<std::string, bool> written;
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    bool& seen = written[path];
+    std::ofstream out(path, std::ios::binary | (seen ? std::ios::app : std::ios::trunc));
+    if (!out.is_open()) throw std::runtime_error("Failed to open rerank stop-prefix trace for writing: " + path);
+    const std::uint32_t header[3] = {kStopPrefixTraceMagic, static_cast<std::uint32_t>(budget_top_n),
+                                     static_cast<std::uint32_t>(prefixes.size())};
+    out.write(reinterpret_cast<const char*>(header), sizeof(header));
+    out.write(reinterpret_cast<const char*>(prefixes.data()), static_cast<std::streamsize>(prefixes.size() * sizeof(std::uint32_t)));
+    if (!out) throw std::runtime_error("Failed to write rerank stop-prefix trace: " + path);
+    seen = true;
+}
+
+std::vector<std::uint32_t> ReadStopPrefixTrace(const std::string& path, std::size_t budget_top_n, std::size_t num_queries) {
+    static std::map<std::string, std::unique_ptr<std::ifstream>> open_files;
+    std::lock_guard<std::mutex> lock(g_trace_mutex);
+    std::unique_ptr<std::ifstream>& in = open_files[path];
+    if (!in) in = std::make_unique<std::ifstream>(path, std::ios::binary);
+    if (!in->is_open()) throw std::runtime_error("Failed to open rerank stop-prefix trace for reading: " + path);
+    std::uint32_t header[3] = {0, 0, 0};
+    in->read(reinterpret_cast<char*>(header), sizeof(header));
+    if (!*in || header[0] != kStopPrefixTraceMagic || header[1] != budget_top_n || header[2] != num_queries)
+        throw std::runtime_error("Rerank stop-prefix trace mismatch or premature EOF: " + path);
+    std::vector<std::uint32_t> prefixes(num_queries);
+    in->read(reinterpret_cast<char*>(prefixes.data()), static_cast<std::streamsize>(prefixes.size() * sizeof(std::uint32_t)));
+    if (!*in) throw std::runtime_error("Truncated rerank stop-prefix trace payload: " + path);
+    return prefixes;
+}
+
+std::string EnvOrEmpty(const char* name) {
+    const char* v = std::getenv(name);
+    return v == nullptr ? std::string{} : std::string(v);
+}
+
+struct DeviceLearnedRerank {
+    std::vector<float> dists;          // [Q][top_k] sorted
+    std::vector<std::uint32_t> ids;
+    std::vector<std::uint32_t> stop_prefixes, checkpoint_counts;
+    std::size_t n_exact = 0, n_filtered = 0;
+    bool evaluated = false;            // the model ran (no replay, model enabled)
+    double kernel_ms = 0.0;
+};
+
+// Host side of the persistent rerank with the learned stop (RunPersistentBamRerankFloat32,
+// src/io/bam_vector_provider.cu:2471-2774): model file, record / replay environment variables, one kernel.
+DeviceLearnedRerank RunLearnedRerankKernel(const TannIndexView& view, const TannRerankParams& rp, const RerankExactParams& params,
+                                           const DeviceCand* cand, std::uint32_t capacity, std::size_t num_queries,
+                                           const void* d_queries, const float* error_bounds) {
+    const char* ctx = "RunPersistentBamRerankFloat32";
+    const std::size_t budget = std::min<std::size_t>(rp.top_n, capacity);
+    const std::string record_path = EnvOrEmpty("TOPOANNS_RERANK_STOP_PREFIX_RECORD_PATH");
+    const std::string replay_path = EnvOrEmpty("TOPOANNS_RERANK_STOP_PREFIX_REPLAY_PATH");
+    if (!record_path.empty() && !replay_path.empty())
+        throw std::runtime_error(BuildErrorMessage(ctx, "Record and replay modes are mutually exclusive."));
+    TannRerankLearnedStop model{};
+    ThrowIfTannError(tann_rerank_learned_stop_load(params.learned_stop_model_path.string().c_str(),
+                                                   static_cast<std::uint32_t>(budget), rp.top_k, &model), ctx);
+    CudaBuffer<std::uint32_t> d_replay;
+    if (!replay_path.empty()) {
+        const std::vector<std::uint32_t> prefixes = ReadStopPrefixTrace(replay_path, budget, num_queries);
+        for (std::uint32_t prefix : prefixes)
+            if (prefix < rp.top_k || prefix > budget) throw std::runtime_error(BuildErrorMessage(ctx, "Invalid replay stop prefix."));
+        d_replay = CudaBuffer<std::uint32_t>::CopyFromHost(prefixes);
+    }
+    DeviceLearnedRerank out;
+    out.evaluated = model.enabled != 0 && replay_path.empty();
+    const std::size_t flat = num_queries * rp.top_k;
+    CudaBuffer<float> d_dists = CudaBuffer<float>::Allocate(flat);
+    CudaBuffer<std::uint32_t> d_ids = CudaBuffer<std::uint32_t>::Allocate(flat);
+    CudaBuffer<unsigned long long> d_counts = CudaBuffer<unsigned long long>::CopyFromHost({0ull, 0ull});
+    CudaBuffer<std::uint32_t> d_prefixes = CudaBuffer<std::uint32_t>::Allocate(num_queries);
+    CudaBuffer<std::uint32_t> d_checkpoints = CudaBuffer<std::uint32_t>::Allocate(num_queries);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    ThrowIfCudaError(cudaEventCreate(&e0), "cudaEventCreate");
+    ThrowIfCudaError(cudaEventCreate(&e1), "cudaEventCreate");
+    ThrowIfCudaError(cudaEventRecord(e0), "cudaEventRecord");
+    const TannStatus st = tann_rerank_exact_learned_stop(&view, &rp, &model, cand, capacity, num_queries, d_queries,
+                                                         TANN_KIND_FLOAT32, error_bounds, replay_path.empty() ? nullptr : d_replay.get(),
+                                                         d_dists.get(), d_ids.get(), d_counts.get(), d_prefixes.get(),
+                                                         d_checkpoints.get(), nullptr, nullptr, nullptr);
+    if (st != TANN_OK) {
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        ThrowIfTannError(st, ctx);
+    }
+    ThrowIfCudaError(cudaEventRecord(e1), "cudaEventRecord");
+    ThrowIfCudaError(cudaEventSynchronize(e1), "cudaEventSynchronize");
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    out.kernel_ms = ms;
+    out.dists = d_dists.CopyToHost();
+    out.ids = d_ids.CopyToHost();
+    out.stop_prefixes = d_prefixes.CopyToHost();
+    out.checkpoint_counts = d_checkpoints.CopyToHost();
+    const std::vector<unsigned long long> counts = d_counts.CopyToHost();
+    out.n_exact = counts[0];
+    out.n_filtered = counts[1];
+    if (out.evaluated && !record_path.empty()) AppendStopPrefixTrace(record_path, budget, out.stop_prefixes);
+    return out;
+}
+
 template <typename QueryT>
 std::uint32_t KindOf();
 template <> std::uint32_t KindOf<float>() { return TANN_KIND_FLOAT32; }
@@ -439,8 +552,20 @@ RerankBatchResult RerankFromDeviceTraversal(const SearchResources& resources, co
         if (params.mode == RerankExecutionMode::kLinear) throw std::runtime_error(BuildErrorMessage(ctx, "PQ2 bound filter requires a non-linear GPU rerank path."));
         if (!resources.has_pq2_error_bounds()) throw std::runtime_error(BuildErrorMessage(ctx, "PQ2 bound filter requires residual PQ2 error bounds."));
     }
-    if (params.use_learned_stop)
-        throw std::runtime_error(BuildErrorMessage(ctx, "the learned rerank stop belongs to the NVMe-backed persistent path and is not available."));
+    if (params.use_learned_stop) {   // src/search/rerank_exact.cu:2586-2602
+        if (params.mode != RerankExecutionMode::kPersistent)
+            throw std::runtime_error(BuildErrorMessage(ctx, "learned rerank stop requires the persistent GPU rerank path."));
+        if (!params.use_pq2_bound_filter)
+            throw std::runtime_error(BuildErrorMessage(ctx, "learned rerank stop requires PQ34 refine + bound filter."));
+        if (params.learned_stop_model_path.empty())
+            throw std::runtime_error(BuildErrorMessage(ctx, "learned rerank stop requires learned_stop_model_path."));
+        if (params.top_k == 0 || params.top_k > 128)
+            throw std::runtime_error(BuildErrorMessage(ctx, "learned rerank stop requires 1 <= top_k <= 128."));
+    } else if (!EnvOrEmpty("TOPOANNS_RERANK_STOP_PREFIX_RECORD_PATH").empty() ||
+               !EnvOrEmpty("TOPOANNS_RERANK_STOP_PREFIX_REPLAY_PATH").empty()) {
+        if (params.mode == RerankExecutionMode::kPersistent)   // src/io/bam_vector_provider.cu:2541-2545
+            throw std::runtime_error(BuildErrorMessage("RunPersistentBamRerankFloat32", "Stop-prefix profiling requires learned stop."));
+    }
     if (params.use_early_stop) {
         if (params.mode != RerankExecutionMode::kPersistent && params.mode != RerankExecutionMode::kTiled)
             throw std::runtime_error(BuildErrorMessage(ctx, "rerank early stop requires the persistent or tiled mode."));
@@ -502,6 +627,70 @@ RerankBatchResult RerankFromDeviceTraversal(const SearchResources& resources, co
                         params.use_pq2_bound_filter ? 1u : 0u, params.use_early_stop ? 1u : 0u,
                         static_cast<std::uint32_t>(params.early_stop_min_prefix),
                         static_cast<std::uint32_t>(params.early_stop_patience_tiles), 0u};
+    if (params.use_learned_stop) {
+        // The persistent rerank keeps only the top_k list per query (result_top_n = top_k,
+        // src/io/bam_vector_provider.cu:2546, src/search/rerank_exact.cu:2202-2228).
+        const DeviceLearnedRerank lr = RunLearnedRerankKernel(view, rp, params, cand, capacity, num_queries, d_queries.get(),
+                                                              resources.pq2_error_bounds_fp32().get());
+        result.stats.exact_distance_count = lr.n_exact;
+        result.stats.bound_filtered_count = lr.n_filtered;
+        result.stats.io_pages = lr.n_exact;
+        const auto t1 = Clock::now();
+        result.queries.resize(num_queries);
+        for (std::size_t q = 0; q < num_queries; ++q) {
+            auto& out = result.queries[q];
+            for (std::size_t r = 0; r < params.top_k; ++r) {
+                const std::uint32_t id = lr.ids[q * params.top_k + r];
+                out.sorted_candidates.push_back(RankedCandidate{lr.dists[q * params.top_k + r], id, id != kInvalidNodeId});
+                if (id != kInvalidNodeId) out.topk.push_back(out.sorted_candidates.back());
+            }
+        }
+        prof.sorted_candidates_materialize_ms = MsSince(t1);
+        prof.exact_distance_kernel_ms = lr.kernel_ms;
+        prof.requested_top_n = params.top_n;
+        prof.effective_top_n = std::min<std::size_t>(params.top_n, capacity);
+        prof.exact_candidates = lr.n_exact;
+        prof.bound_filtered_candidates = lr.n_filtered;
+        prof.rerank_batches = 1;
+        prof.rerank_tile_size = tile;
+        if (lr.evaluated) {
+            prof.learned_stop_queries = num_queries;
+            prof.learned_stop_prefix_min = prof.effective_top_n;
+            for (std::size_t q = 0; q < num_queries; ++q) {
+                prof.learned_stop_checkpoints += lr.checkpoint_counts[q];
+                prof.learned_stop_prefix_sum += lr.stop_prefixes[q];
+                prof.learned_stop_prefix_min = std::min<std::size_t>(prof.learned_stop_prefix_min, lr.stop_prefixes[q]);
+                prof.learned_stop_prefix_max = std::max<std::size_t>(prof.learned_stop_prefix_max, lr.stop_prefixes[q]);
+            }
+        }
+        prof.total_ms = MsSince(total_begin);
+        if (out_profile != nullptr) {
+            out_profile->total_ms += prof.total_ms;
+            out_profile->pq2_refine_kernel_ms += prof.pq2_refine_kernel_ms;
+            out_profile->pq2_refine_batches += prof.pq2_refine_batches;
+            out_profile->pq2_residual_refine_batches += prof.pq2_residual_refine_batches;
+            out_profile->exact_distance_kernel_ms += prof.exact_distance_kernel_ms;
+            out_profile->exact_candidates += prof.exact_candidates;
+            out_profile->bound_filtered_candidates += prof.bound_filtered_candidates;
+            out_profile->rerank_batches += 1;
+            out_profile->requested_top_n += prof.requested_top_n;
+            out_profile->effective_top_n += prof.effective_top_n;
+            out_profile->sorted_candidates_materialize_ms += prof.sorted_candidates_materialize_ms;
+            out_profile->learned_stop_checkpoints += prof.learned_stop_checkpoints;
+            out_profile->learned_stop_queries += prof.learned_stop_queries;
+            out_profile->learned_stop_prefix_sum += prof.learned_stop_prefix_sum;
+            if (prof.learned_stop_prefix_max != 0 || prof.learned_stop_prefix_min != 0) {
+                if (out_profile->learned_stop_prefix_max == 0 && out_profile->learned_stop_prefix_min == 0) {
+                    out_profile->learned_stop_prefix_min = prof.learned_stop_prefix_min;
+                    out_profile->learned_stop_prefix_max = prof.learned_stop_prefix_max;
+                } else {
+                    out_profile->learned_stop_prefix_min = std::min(out_profile->learned_stop_prefix_min, prof.learned_stop_prefix_min);
+                    out_profile->learned_stop_prefix_max = std::max(out_profile->learned_stop_prefix_max, prof.learned_stop_prefix_max);
+                }
+            }
+        }
+        return result;
+    }
     const DeviceRerank rr = RunRerankKernel(resources, view, rp, cand, capacity, num_queries, d_queries.get(),
                                             TANN_KIND_FLOAT32,
                                             params.use_pq2_bound_filter ? resources.pq2_error_bounds_fp32().get() : nullptr, ctx);

@@ -287,6 +287,40 @@ def rerank_exact(index: DeviceIndex, params: RerankExactParams, cand: torch.Tens
     return dists, ids, int(c[0]), int(c[1])
 
 
+def load_rerank_learned_stop(path, budget_top_n: int, top_k: int) -> capi.RerankLearnedStop:
+    """Reads a learned rerank-stop model file and folds it for a budget of budget_top_n ranks
+    (LoadRerankLearnedStopConfigFromFile, src/io/bam_vector_provider.cu:125-279)."""
+    model = capi.RerankLearnedStop()
+    capi.check(capi.load().tann_rerank_learned_stop_load(str(path).encode(), budget_top_n, top_k, C.byref(model)))
+    return model
+
+
+def rerank_exact_learned_stop(index: DeviceIndex, params: RerankExactParams, cand: torch.Tensor,
+                              queries: torch.Tensor, model: Optional[capi.RerankLearnedStop] = None,
+                              replay_stop_prefixes: Optional[torch.Tensor] = None,
+                              error_bounds: Optional[torch.Tensor] = None):
+    """The reference's persistent rerank (src/io/bam_vector_provider.cu:721-1323): top_k list per query,
+    learned stage schedule and stop, or stop-prefix replay. Returns a dict: dists / ids [Q, top_k],
+    stop_prefixes / checkpoint_counts / stop_flags [Q] (device tensors), n_exact, n_filtered."""
+    Q, capacity, _ = cand.shape
+    dev = cand.device
+    dists = torch.empty((Q, params.top_k), dtype=torch.float32, device=dev)
+    ids = torch.empty((Q, params.top_k), dtype=torch.int32, device=dev)
+    counts = torch.zeros(2, dtype=torch.int64, device=dev)
+    stop_prefixes = torch.zeros(Q, dtype=torch.int32, device=dev)
+    checkpoints = torch.zeros(Q, dtype=torch.int32, device=dev)
+    flags = torch.zeros(Q, dtype=torch.int32, device=dev)
+    view = index.view()
+    p = params.to_c()
+    capi.check(capi.load().tann_rerank_exact_learned_stop(
+        C.byref(view), C.byref(p), C.byref(model) if model is not None else None, _ptr(cand), capacity, Q,
+        _ptr(queries), kind_of(queries), _ptr(error_bounds), _ptr(replay_stop_prefixes), _ptr(dists), _ptr(ids),
+        _ptr(counts), _ptr(stop_prefixes), _ptr(checkpoints), _ptr(flags), None, _stream_ptr()))
+    c = counts.cpu()
+    return dict(dists=dists, ids=ids, stop_prefixes=stop_prefixes, checkpoint_counts=checkpoints, stop_flags=flags,
+                n_exact=int(c[0]), n_filtered=int(c[1]))
+
+
 def topk_pack(dists, ids, top_k):
     Q, top_n = dists.shape
     od = torch.empty((Q, top_k), dtype=torch.float32, device=dists.device)
