@@ -325,6 +325,110 @@ void TestPq2() {
     CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {1.0f, 1.0f}, 1, p));
 }
 
+void TestLearnedRerankStop() {
+    // Persistent rerank with the learned stop (src/io/bam_vector_provider.cu:721-1323, :2471-2774) through the
+    // fused entry point. 24 nodes on a line, query at 0: node i is at i + 1 (exact distance (i + 1)^2) but its
+    // PQ code says 24 - i, so the candidate list is ranked 23, 22, ..., 0 and every window of four ranks
+    // improves the best-2 list. Error bounds of 100 make every lower bound 0: nothing is filtered.
+    const std::size_t n = 24;
+    std::vector<std::uint8_t> base_codes(n), zero_codes(n, 0);
+    std::vector<float> eps(n, 100.0f);
+    std::vector<std::vector<std::uint8_t>> rows;
+    std::vector<std::vector<std::uint32_t>> lists(n);
+    for (std::size_t i = 0; i < n; ++i) {
+        base_codes[i] = static_cast<std::uint8_t>(n - i);
+        rows.push_back(fx::FloatBytes({static_cast<float>(i + 1)}));
+        if (i > 0) lists[0].push_back(static_cast<std::uint32_t>(i));
+    }
+    fx::WritePq(fx::Tmp("ls_base_pivots.bin"), fx::Tmp("ls_base_codes.bin"), 1, fx::RampTables(1), base_codes);
+    fx::WritePq(fx::Tmp("ls_res_pivots.bin"), fx::Tmp("ls_res_codes.bin"), 1, std::vector<float>(256, 0.0f), zero_codes);
+    fx::WriteErrorBounds(fx::Tmp("ls_eps.bin"), eps);
+    SearchResources r = SearchResources::FromDataset(TopologyLayout::MakePadded(n, lists));
+    r.LoadPqIndex(fx::Tmp("ls_base_pivots.bin"), fx::Tmp("ls_base_codes.bin"));
+    r.LoadPq2Index(fx::Tmp("ls_res_pivots.bin"), fx::Tmp("ls_res_codes.bin"), fx::Tmp("ls_eps.bin"));
+    const VectorPageLayout layout = VectorPageLayout::Create(1, ScalarKind::kFloat32);
+    VectorStoreBuilder::WriteFile(fx::Tmp("ls_vectors.ssd"), layout, ScalarKind::kFloat32, 1, rows);
+    r.LoadVectorStore(fx::Tmp("ls_vectors.ssd"));
+    r.AttachVectorPageProvider(std::make_shared<HbmVectorPageProvider>(fx::Tmp("ls_vectors.ssd")));
+    // logit = 1 - 4 * (ranks scored / 24): 1/3 after the bootstrap window (no stage there), -1/3 at the
+    // stage at 8, -1 at the stage at 12, which is below the threshold -0.5.
+    {
+        std::ofstream model(fx::Tmp("ls_model.txt"));
+        model << "# synthetic model\nstage_prefixes = 8, 12, 16\nbootstrap_prefix = 4\n"
+              << "feature_means = 0,0,0,0,0,0,0,0,0,0,0,0,0\nfeature_inv_stds = 1,1,1,1,1,1,1,1,1,1,1,1,1\n"
+              << "weights = 0,-4,0,0,0,0,0,0,0,0,0,0,0\nbias = 1\nthreshold_logit = -0.5\n";
+    }
+    TopoAnnsSearchParams p;
+    p.topology.top_k = 24; p.topology.top_l = 24; p.topology.search_width = 1; p.topology.max_expansions = 64;
+    p.rerank.top_k = 2; p.rerank.top_n = 24; p.rerank.mode = RerankExecutionMode::kPersistent; p.rerank.rank_tile_size = 4;
+    p.rerank.use_pq2_refine = true; p.rerank.use_pq2_bound_filter = true; p.rerank.pq2_refine_top_l = 24;
+    p.rerank.use_learned_stop = true; p.rerank.learned_stop_model_path = fx::Tmp("ls_model.txt");
+    unsetenv("TOPOANNS_RERANK_STOP_PREFIX_RECORD_PATH");
+    unsetenv("TOPOANNS_RERANK_STOP_PREFIX_REPLAY_PATH");
+    const auto check_stopped_at_12 = [&](const TopoAnnsBatchResult& res) {
+        CHECK_EQ(res.rerank_stats.exact_distance_count, std::size_t{12});
+        CHECK_EQ(res.rerank_stats.bound_filtered_count, std::size_t{0});
+        CHECK_EQ(res.queries[0].rerank.sorted_candidates.size(), std::size_t{2});   // the top_k list only
+        CHECK_EQ(res.queries[0].rerank.topk.size(), std::size_t{2});
+        CHECK_EQ(res.queries[0].rerank.topk[0].node_id, 12u);
+        CHECK_EQ(res.queries[0].rerank.topk[0].distance, 169.0f);
+        CHECK_EQ(res.queries[0].rerank.topk[1].node_id, 13u);
+        CHECK_EQ(res.queries[0].rerank.topk[1].distance, 196.0f);
+    };
+    const auto res = TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p);
+    check_stopped_at_12(res);
+    CHECK_EQ(res.rerank_profile.learned_stop_queries, std::size_t{1});
+    CHECK_EQ(res.rerank_profile.learned_stop_checkpoints, std::size_t{2});
+    CHECK_EQ(res.rerank_profile.learned_stop_prefix_sum, std::size_t{12});
+    CHECK_EQ(res.rerank_profile.learned_stop_prefix_min, std::size_t{12});
+    CHECK_EQ(res.rerank_profile.learned_stop_prefix_max, std::size_t{12});
+    // record the stop prefixes of two batches, then replay them: same lists, the model is not evaluated
+    const std::string trace = fx::Tmp("ls_trace.bin").string();
+    setenv("TOPOANNS_RERANK_STOP_PREFIX_RECORD_PATH", trace.c_str(), 1);
+    check_stopped_at_12(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p));
+    check_stopped_at_12(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p));
+    CHECK_EQ(std::filesystem::file_size(trace), std::uintmax_t{2 * (12 + 4)});
+    setenv("TOPOANNS_RERANK_STOP_PREFIX_REPLAY_PATH", trace.c_str(), 1);
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p));   // both set
+    unsetenv("TOPOANNS_RERANK_STOP_PREFIX_RECORD_PATH");
+    for (int batch = 0; batch < 2; ++batch) {
+        const auto again = TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p);
+        check_stopped_at_12(again);
+        CHECK_EQ(again.rerank_profile.learned_stop_queries, std::size_t{0});
+        CHECK_EQ(again.rerank_profile.learned_stop_checkpoints, std::size_t{0});
+    }
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, p));   // the trace has two records
+    unsetenv("TOPOANNS_RERANK_STOP_PREFIX_REPLAY_PATH");
+    // a threshold that nothing reaches: every rank is scored, the list is the true best two
+    {
+        std::ofstream model(fx::Tmp("ls_model_never.txt"));
+        model << "stage_prefixes = 8, 12, 16\nbootstrap_prefix = 4\nfeature_means = 0,0,0,0,0,0,0,0,0,0,0,0,0\n"
+              << "feature_inv_stds = 1,1,1,1,1,1,1,1,1,1,1,1,1\nweights = 0,-4,0,0,0,0,0,0,0,0,0,0,0\nbias = 1\n"
+              << "threshold_logit = -100\n";
+    }
+    TopoAnnsSearchParams never = p;
+    never.rerank.learned_stop_model_path = fx::Tmp("ls_model_never.txt");
+    const auto full = TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, never);
+    CHECK_EQ(full.rerank_stats.exact_distance_count, std::size_t{24});
+    CHECK_EQ(full.queries[0].rerank.topk[0].node_id, 0u);
+    CHECK_EQ(full.queries[0].rerank.topk[1].node_id, 1u);
+    CHECK_EQ(full.rerank_profile.learned_stop_checkpoints, std::size_t{3});
+    CHECK_EQ(full.rerank_profile.learned_stop_prefix_sum, std::size_t{24});
+    // the reference's parameter checks (src/search/rerank_exact.cu:2586-2602)
+    TopoAnnsSearchParams bad = p;
+    bad.rerank.mode = RerankExecutionMode::kTiled;
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, bad));
+    bad = p;
+    bad.rerank.use_pq2_bound_filter = false;
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, bad));
+    bad = p;
+    bad.rerank.learned_stop_model_path.clear();
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, bad));
+    bad = p;
+    bad.rerank.learned_stop_model_path = fx::Tmp("ls_no_such_model.txt");
+    CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {0.0f}, 1, bad));
+}
+
 void TestRvqModel() {
     // two coarse x two fine centroids in 2-d; model file in the reference's layout
     const auto path = fx::Tmp("rvq_model.bin");
@@ -378,6 +482,7 @@ int main() {
     TestRerankAndEndToEnd();
     TestUint8EntryPoint();
     TestPq2();
+    TestLearnedRerankStop();
     TestRvqModel();
     std::cout << "test_api_search passed" << std::endl;
     return 0;

@@ -30,16 +30,20 @@ def test_cpp_search_api(tmp_path):
     _run("test_api_search", tmp_path)
 
 
-def _write_index_dir(tmp_path):
+def _write_index_dir(tmp_path, name="cfg2", num_nodes=40000, components=40):
     """A small RVQ-entry index written in the reference's file layouts; returns what the tests need."""
     import numpy as np
 
     from gpu_support import small_index
     from topoanns_b200 import formats
 
-    s, host = small_index(name="cfg2", num_nodes=40000, components=40, num_queries=300)
+    s, host = small_index(name=name, num_nodes=num_nodes, components=components, num_queries=300)
     d = tmp_path / "index"
     d.mkdir()
+    if host.get("pq2_tables") is not None:
+        formats.write_pq(tmp_path / "pq2_pivots.bin", tmp_path / "pq2_codes.bin", host["pq2_tables"], host["pq2_centroid"],
+                         host["pq_chunk_offsets"], host["pq2_codes"])
+        formats.write_error_bounds(tmp_path / "pq2_eps.bin", host["pq2_error_bounds"])
     formats.write_topology(d / "topology.bin", host["adjacency"])
     formats.write_pq(d / "_pq_pivots.bin", d / "_pq_compressed.bin", host["pq_tables"], host["pq_centroid"],
                      host["pq_chunk_offsets"], host["codes"])
@@ -173,3 +177,42 @@ def test_learned_stop_model_file_and_early_stop_through_the_driver(tmp_path):
                                     "--rerank-rank-tile-size", "8"], capture_output=True, text=True, timeout=600)
     assert r2.returncode == 0, r2.stdout + r2.stderr
     assert _summaries(r2.stdout)[64]["avg_exact"] < 64.0
+
+
+@pytest.mark.gpu
+def test_learned_rerank_stop_through_the_driver(tmp_path):
+    """--rerank-use-learned-stop / --rerank-learned-stop-model on a float index with residual pq2 and error
+    bounds: the summary line carries the learned-stop keys, a model that stops early scores fewer candidates,
+    and a model whose threshold nothing reaches gives the recall of the plain persistent rerank."""
+    import re
+
+    _build()
+    s, q, gt, base_cmd = _write_index_dir(tmp_path, name="cfg3", num_nodes=12000, components=60)
+    pq2 = ["--pq2-pivots", str(tmp_path / "pq2_pivots.bin"), "--pq2-codes", str(tmp_path / "pq2_codes.bin"),
+           "--pq2-error-bounds", str(tmp_path / "pq2_eps.bin"), "--rerank-use-pq2", "--rerank-use-pq2-bound-filter",
+           "--rerank-mode", "persistent", "--rerank-rank-tile-size", "16", "--top-l-values", "128", "--rerank-top-n", "128"]
+
+    def model(name, threshold):
+        path = tmp_path / name
+        path.write_text("stage_prefixes = 16, 32, 64, 96\nbootstrap_prefix = 16\n"
+                        "feature_means = 0,0,0,0,0,0,0,0,0,0,0,0,0\nfeature_inv_stds = 1,1,1,1,1,1,1,1,1,1,1,1,1\n"
+                        "weights = 0,-4,0,0,0,0,1,0,0,0,0,0,0\nbias = 1\nthreshold_logit = %g\n" % threshold)
+        return str(path)
+
+    def run(extra):
+        r = subprocess.run(base_cmd + pq2 + extra, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout + r.stderr
+        line = [l for l in r.stdout.splitlines() if " elapsed_sec=" in l][-1]
+        return dict(kv.split("=", 1) for kv in line.split()[1:] if "=" in kv)
+
+    plain = run([])
+    stop = run(["--rerank-use-learned-stop", "--rerank-learned-stop-model", model("stop.model", 0.0)])
+    never = run(["--rerank-use-learned-stop", "--rerank-learned-stop-model", model("never.model", -1000.0)])
+    assert "learned_stop_queries" not in plain
+    assert int(stop["learned_stop_queries"]) == q.shape[0]
+    assert 16 <= int(stop["learned_stop_prefix_min"]) <= int(stop["learned_stop_prefix_max"]) <= 128
+    assert float(stop["avg_learned_stop_prefix"]) < 128 and float(stop["avg_learned_checkpoints"]) >= 1
+    assert float(stop["avg_exact"]) < float(never["avg_exact"])
+    assert float(never["avg_learned_stop_prefix"]) == 128.0 and float(never["avg_learned_checkpoints"]) == 3.0
+    assert abs(float(never["recall@10"]) - float(plain["recall@10"])) < 1e-9
+    assert re.match(r"^\d+(\.\d+)?$", stop["avg_learned_stop_prefix"])

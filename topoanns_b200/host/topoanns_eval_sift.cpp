@@ -34,6 +34,8 @@ struct Args {
     topoanns::RerankExecutionMode rerank_mode = topoanns::RerankExecutionMode::kPersistent;
     bool use_pq2_refine = false, use_pq2_bound_filter = false, use_early_stop = false;
     std::size_t early_stop_min_prefix = 32, early_stop_patience_tiles = 1;
+    bool use_learned_stop = false;
+    std::filesystem::path learned_stop_model;
     std::string vector_residency = "hbm", topology_residency = "hbm";
     std::uint64_t topology_cached_rows = 0;
     std::size_t repeats = 1;
@@ -59,8 +61,8 @@ struct SweepPoint {
                  " [--rerank-early-stop-min-prefix <count>] [--rerank-early-stop-patience-tiles <count>] [--max-expansions <count>] [--rvq-entry-count <count>]"
                  " [--vector-residency <hbm|pinned-host>] [--topology-residency <hbm|pinned-host>]"
                  " [--topology-cached-rows <count>] [--repeats <count>] [--neighbor-code-layout]"
-                 " (flags of the NVMe backend, --bam-*, --frontier-pq-modes and the learned rerank stop flags are accepted"
-                 " and ignored)"
+                 " [--rerank-use-learned-stop --rerank-learned-stop-model <path>]"
+                 " (flags of the NVMe backend, --bam-* and --frontier-pq-modes, are accepted and ignored)"
               << std::endl;
     std::exit(1);
 }
@@ -97,9 +99,8 @@ Args Parse(int argc, char** argv) {
     // flags with one value that this library has no use for
     const char* ignored_with_value[] = {"--frontier-pq-modes", "--bam-config-path", "--bam-controller-path",
                                         "--bam-device-offset-bytes", "--bam-page-cache-bytes", "--bam-queue-depth",
-                                        "--bam-num-queues", "--bam-cuda-device", "--rerank-mode-sweep",
-                                        "--rerank-learned-stop-model"};
-    const char* ignored_flags[] = {"--allow-bam-controller-override", "--rerank-use-learned-stop"};
+                                        "--bam-num-queues", "--bam-cuda-device", "--rerank-mode-sweep"};
+    const char* ignored_flags[] = {"--allow-bam-controller-override"};
     for (int i = 1; i < argc; ++i) {
         const std::string f = argv[i];
         auto value = [&]() -> std::string {
@@ -133,6 +134,8 @@ Args Parse(int argc, char** argv) {
         else if (f == "--rerank-use-pq2") a.use_pq2_refine = true;
         else if (f == "--rerank-use-pq2-bound-filter") a.use_pq2_bound_filter = true;
         else if (f == "--rerank-use-early-stop") a.use_early_stop = true;
+        else if (f == "--rerank-use-learned-stop") a.use_learned_stop = true;
+        else if (f == "--rerank-learned-stop-model") a.learned_stop_model = value();
         else if (f == "--rerank-early-stop-min-prefix") a.early_stop_min_prefix = std::stoull(value());
         else if (f == "--rerank-early-stop-patience-tiles") a.early_stop_patience_tiles = std::stoull(value());
         else if (f == "--max-expansions") a.max_expansions = std::stoull(value());
@@ -146,6 +149,10 @@ Args Parse(int argc, char** argv) {
     }
     if (a.index_dir.empty() || a.rvq_model.empty() || a.query_bin.empty() || a.num_queries == 0 || a.top_l_values.empty())
         Usage();
+    if (a.use_learned_stop && a.learned_stop_model.empty())
+        throw std::runtime_error("rerank-use-learned-stop requires rerank-learned-stop-model.");
+    if (a.use_learned_stop && a.use_early_stop)
+        throw std::runtime_error("rerank-use-learned-stop cannot be combined with rerank-use-early-stop.");
     if (a.eval_query_counts.empty()) a.eval_query_counts.push_back(a.num_queries);
     if (!a.rerank_top_n_values.empty() && a.rerank_top_n_values.size() != a.top_l_values.size())
         throw std::runtime_error("--rerank-top-n-values must have one value per --top-l-values entry.");
@@ -251,11 +258,15 @@ int main(int argc, char** argv) {
                     params.rerank.use_early_stop = args.use_early_stop;
                     params.rerank.early_stop_min_prefix = args.early_stop_min_prefix;
                     params.rerank.early_stop_patience_tiles = args.early_stop_patience_tiles;
+                    params.rerank.use_learned_stop = args.use_learned_stop;
+                    params.rerank.learned_stop_model_path = args.learned_stop_model;
+                    std::size_t stop_queries = 0, stop_prefix_sum = 0, stop_prefix_min = 0, stop_prefix_max = 0, stop_checkpoints = 0;
                     double best_elapsed = 0.0, recall = -1.0;
                     std::size_t io_pages = 0, exact = 0, filtered = 0, visited = 0, expanded = 0;
                     for (std::size_t rep = 0; rep < args.repeats; ++rep) {   // the first pass is the cold one
                         double recall_sum = 0.0;
                         io_pages = exact = filtered = visited = expanded = 0;
+                        stop_queries = stop_prefix_sum = stop_prefix_min = stop_prefix_max = stop_checkpoints = 0;
                         const auto start = std::chrono::steady_clock::now();
                         for (std::size_t off = 0; off < eval_queries; off += batch) {
                             const std::size_t n = std::min(batch, eval_queries - off);
@@ -268,6 +279,14 @@ int main(int argc, char** argv) {
                             io_pages += result.rerank_stats.io_pages;
                             exact += result.rerank_stats.exact_distance_count;
                             filtered += result.rerank_stats.bound_filtered_count;
+                            const topoanns::RerankBatchProfile& rp = result.rerank_profile;
+                            if (rp.learned_stop_queries != 0) {
+                                stop_prefix_min = stop_queries == 0 ? rp.learned_stop_prefix_min : std::min(stop_prefix_min, rp.learned_stop_prefix_min);
+                                stop_prefix_max = std::max(stop_prefix_max, rp.learned_stop_prefix_max);
+                                stop_queries += rp.learned_stop_queries;
+                                stop_prefix_sum += rp.learned_stop_prefix_sum;
+                                stop_checkpoints += rp.learned_stop_checkpoints;
+                            }
                             for (const auto& q : result.queries) {
                                 visited += q.topology.stats.visited_nodes;
                                 expanded += q.topology.stats.expanded_nodes;
@@ -289,7 +308,12 @@ int main(int argc, char** argv) {
                               << " wall_qps=" << qps;
                     if (recall >= 0.0) std::cout << " recall@10=" << recall;
                     std::cout << " avg_io_pages=" << io_pages / nq << " avg_exact=" << exact / nq << " avg_bound_filtered=" << filtered / nq
-                              << " avg_visited=" << visited / nq << " avg_expanded=" << expanded / nq << std::endl;
+                              << " avg_visited=" << visited / nq << " avg_expanded=" << expanded / nq;
+                    if (args.use_learned_stop)   // tools/topoanns_eval_sift.cpp:804-857
+                        std::cout << " avg_learned_checkpoints=" << stop_checkpoints / nq << " learned_stop_queries=" << stop_queries
+                                  << " avg_learned_stop_prefix=" << stop_prefix_sum / nq << " learned_stop_prefix_min=" << stop_prefix_min
+                                  << " learned_stop_prefix_max=" << stop_prefix_max;
+                    std::cout << std::endl;
                     sweep.push_back(SweepPoint{top_l, rerank_top_n, args.rerank_mode, eval_queries, qps, qps, recall});
                 }
             }
