@@ -199,6 +199,21 @@ TannStatus tann_pq2_refine(const void* candidates /*dev [Q][capacity]*/,
                            const float* cross_terms /*dev [M][256][256] or NULL*/,
                            void* out_candidates /*dev*/, uint32_t* status, tann_stream_t stream);
 
+/*
+ * Hybrid-PQ (HPQ) refine and re-sort of the first refine_top_l candidates of every query. Replaces
+ * detail::RunHpqRefineBatchDevice (src/search/rerank_exact.cu:2457-2531; kernel :667-771): every node has one
+ * code per chunk and one selector bit per chunk (row of (M + 7) / 8 bytes, bit m & 7 of byte m >> 3); the bit
+ * picks the base or the outlier codebook's query table for that chunk; distance = lane-strided sums + shuffle
+ * tree. hybrid_codes and selector_bits may live in device memory or mapped pinned host memory (the reference:
+ * mapped host memory only). Output as tann_pq2_refine.
+ */
+TannStatus tann_hpq_refine(const void* candidates /*dev [Q][capacity]*/, const uint32_t* stats /*dev [Q][8]*/,
+                           uint64_t num_queries, uint32_t capacity, uint32_t refine_top_l,
+                           const TannShards* hybrid_codes, const uint8_t* selector_bits /*[N][(M+7)/8]*/,
+                           uint32_t num_chunks, const float* base_lut /*dev [Q][M][256]*/,
+                           const float* outlier_lut /*dev [Q][M][256]*/, void* out_candidates /*dev*/,
+                           uint32_t* status, tann_stream_t stream);
+
 /* X[m][b][r] = 2 * sum_dim (T1[b][dim]+mu1[dim]) * (T2[r][dim]+mu2[dim]); replaces the host loop
  * BuildPq2CrossTerms (src/search/search_resources.cpp:52-91), same order, no FMA. */
 TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks,

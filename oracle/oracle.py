@@ -182,6 +182,21 @@ def pq2_refine(cand, stats, refine_top_l, pq2_codes, lut2, base_codes=None, cros
     return out
 
 
+def hpq_refine(cand, stats, refine_top_l, hybrid_codes, selector_bits, base_lut, outlier_lut):
+    """Hybrid-PQ refine (src/search/rerank_exact.cu:667-771). Returns [Q, refine_top_l, 2] uint32 records."""
+    cand = _c(cand, np.uint32)
+    stats = _c(stats, np.uint32)
+    Q, capacity, _ = cand.shape
+    codes = _c(hybrid_codes, np.uint8)
+    M = codes.shape[1]
+    sel = _c(selector_bits, np.uint8)
+    assert sel.shape == (codes.shape[0], (M + 7) // 8)
+    out = np.empty((Q, refine_top_l, 2), np.uint32)
+    lib().orc_hpq_refine(_p(cand), _p(stats), C.c_uint64(Q), C.c_uint32(capacity), C.c_uint32(refine_top_l), _p(codes),
+                         _p(sel), C.c_uint32(M), _p(_c(base_lut, np.float32)), _p(_c(outlier_lut, np.float32)), _p(out))
+    return out
+
+
 def exact_distance(query, vec):
     query = np.ascontiguousarray(query)
     vec = np.ascontiguousarray(vec)

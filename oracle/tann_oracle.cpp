@@ -761,6 +761,47 @@ void orc_rerank(const void* cand_in, uint64_t Q, uint32_t capacity, uint32_t top
     if (counts) { counts[0] += n_exact; counts[1] += n_filtered; }
 }
 
+// Hybrid-PQ refine + re-sort, src/search/rerank_exact.cu:667-771: one code per chunk, one selector bit per
+// chunk (bit m & 7 of byte m >> 3 of the node's row) choosing the base or the outlier query table;
+// lanes take chunks lane, lane + 32, ...; tree sum; sort by (distance, id).
+void orc_hpq_refine(const void* cand_in, const uint32_t* stats, uint64_t Q, uint32_t capacity,
+                    uint32_t refine_top_l, const uint8_t* hybrid_codes, const uint8_t* selector_bits, uint32_t M,
+                    const float* base_lut, const float* outlier_lut, void* cand_out) {
+    const Cand* in = static_cast<const Cand*>(cand_in);
+    Cand* out = static_cast<Cand*>(cand_out);
+    const uint32_t stride = (M + 7) / 8;
+    for (uint64_t q = 0; q < Q; ++q) {
+        const uint32_t valid = std::min(stats[q * 8 + 4], refine_top_l);
+        const float* tables[2] = {base_lut + q * M * kCentroids, outlier_lut + q * M * kCentroids};
+        std::vector<Cand> v(refine_top_l);
+        for (uint32_t rank = 0; rank < refine_top_l; ++rank) {
+            Cand o{std::numeric_limits<float>::infinity(), kInvalid};
+            if (rank < valid) {
+                const uint32_t id = RawId(in[q * capacity + rank].id);
+                o.id = id;
+                if (id != kInvalid) {
+                    float lane[32];
+                    for (uint32_t l = 0; l < 32; ++l) {
+                        float partial = 0.0f;
+                        for (uint32_t m = l; m < M; m += 32) {
+                            const uint32_t bit = (selector_bits[(uint64_t)id * stride + (m >> 3)] >> (m & 7)) & 1u;
+                            partial += tables[bit][m * kCentroids + hybrid_codes[(uint64_t)id * M + m]];
+                        }
+                        lane[l] = partial;
+                    }
+                    o.dist = WarpTree(lane);
+                }
+            }
+            v[rank] = o;
+        }
+        std::sort(v.begin(), v.end(), [](const Cand& a, const Cand& b) {
+            if (a.dist != b.dist) return a.dist < b.dist;
+            return a.id < b.id;
+        });
+        for (uint32_t i = 0; i < refine_top_l; ++i) out[q * refine_top_l + i] = v[i];
+    }
+}
+
 // Folded learned rerank-stop model, field for field the reference's DeviceRerankLearnedStopConfig
 // (src/io/bam_vector_provider.cu:65-79).
 struct OrcRerankStop {

@@ -505,6 +505,38 @@ def test_pq2_refine_and_bound_filter_float32():
         assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
 
 
+def test_hpq_refine_matches_checker():
+    """Hybrid-PQ refine (src/search/rerank_exact.cu:667-771): per chunk a selector bit picks the base or the
+    outlier codebook's query table. The second codebook of the float configuration stands in for the outlier
+    codebook; selector bits are random. With all bits clear it is the plain refine with the base table."""
+    s, host = small_index(name="cfg3", num_nodes=12000, components=60, num_queries=128)
+    ix = device_index(s)
+    q = s.queries.cuda().contiguous()
+    Q = q.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid])
+    p = search.TopologySearchParams(top_l=64, search_width=2, max_expansions=2048)
+    cand, stats = search.beam_search(ix, p, eo, ei, queries=q)
+    off = ix.pq_chunk_offsets
+    base_lut = search.lut_build(ix, q)
+    outlier_lut = search.lut_build(ix, q, tables_col_major=s.pq2_tables.cuda().t().contiguous(),
+                                   centroid=s.pq2_centroid.cuda().contiguous(), chunk_offsets=off)
+    N, M = host["codes"].shape
+    rng = np.random.default_rng(11)
+    bits = rng.integers(0, 2, size=(N, M), dtype=np.uint8)
+    hybrid = np.where(bits == 1, host["pq2_codes"], host["codes"]).astype(np.uint8)
+    selectors = np.packbits(bits, axis=1, bitorder="little")
+    assert selectors.shape == (N, (M + 7) // 8)
+    for lr in (64, 48):
+        got = search.hpq_refine(cand, stats, lr, _dev(hybrid), _dev(selectors), base_lut, outlier_lut)
+        want = orc.hpq_refine(np_u32(cand), np_u32(stats), lr, hybrid, selectors, base_lut.cpu().numpy(),
+                              outlier_lut.cpu().numpy())
+        assert np.array_equal(np_u32(got), want)
+    zero = np.zeros_like(selectors)
+    got = search.hpq_refine(cand, stats, 64, ix.codes, _dev(zero), base_lut, outlier_lut)
+    plain = search.pq2_refine(cand, stats, 64, ix.codes, base_lut)
+    assert torch.equal(got, plain)
+
+
 def test_sharded_and_cached_providers_give_the_same_result():
     s, host = small_index()
     ix = device_index(s)

@@ -110,6 +110,7 @@ SIGNATURES = {
                               _U32, _VP, _VP, _VP, _VP]),
     "tann_pq2_refine": (_I, [_VP, _VP, _U64, _U32, _U32, C.POINTER(Shards), C.POINTER(Shards), _U32, _VP,
                              _VP, _VP, _VP, _VP]),
+    "tann_hpq_refine": (_I, [_VP, _VP, _U64, _U32, _U32, C.POINTER(Shards), _VP, _U32, _VP, _VP, _VP, _VP, _VP]),
     "tann_pq2_cross_terms": (_I, [_U32, _U32, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "tann_rerank_exact": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                _VP, _VP, _VP, _VP, _VP, _VP]),

@@ -263,6 +263,24 @@ TannStatus tann_pq2_refine(const void* candidates, const uint32_t* stats, uint64
     return TANN_OK;
 }
 
+TannStatus tann_hpq_refine(const void* candidates, const uint32_t* stats, uint64_t num_queries, uint32_t capacity,
+                           uint32_t refine_top_l, const TannShards* hybrid_codes, const uint8_t* selector_bits,
+                           uint32_t num_chunks, const float* base_lut, const float* outlier_lut, void* out_candidates,
+                           uint32_t* status, tann_stream_t stream) {
+    (void)status;
+    if (num_queries == 0 || refine_top_l == 0) return TANN_OK;
+    if (!candidates || !stats || !hybrid_codes || !selector_bits || !base_lut || !outlier_lut || !out_candidates)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_hpq_refine: HPQ index must be loaded.");
+    // src/search/rerank_exact.cu:2483-2492
+    if (num_chunks > 256) return Fail(TANN_ERR_UNSUPPORTED, "tann_hpq_refine: HPQ layout exceeds kernel limits.");
+    if (refine_top_l > capacity || refine_top_l > 2048)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_hpq_refine: HPQ refine size exceeds candidate limits.");
+    TANN_CUDA(tann::LaunchPq2Refine(candidates, stats, num_queries, capacity, refine_top_l, nullptr, *hybrid_codes,
+                                    num_chunks, base_lut, nullptr, out_candidates, (cudaStream_t)stream, nullptr, nullptr,
+                                    nullptr, nullptr, 0, selector_bits, (num_chunks + 7u) / 8u, outlier_lut));
+    return TANN_OK;
+}
+
 TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks, const uint32_t* chunk_offsets,
                                 const float* tables1_row_major, const float* centroid1,
                                 const float* tables2_row_major, const float* centroid2, float* out,

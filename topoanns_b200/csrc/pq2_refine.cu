@@ -37,7 +37,9 @@ pq2_refine_kernel(const Cand* __restrict__ cand, const uint32_t* __restrict__ st
                   TannShards pq2_codes, uint32_t M, const float* __restrict__ lut2,
                   const float* __restrict__ cross, Cand* __restrict__ out,
                   const float* __restrict__ t2_col_major, const float* __restrict__ mu2,
-                  const uint32_t* __restrict__ chunk_offsets, const float* __restrict__ queries_f32, uint32_t dim) {
+                  const uint32_t* __restrict__ chunk_offsets, const float* __restrict__ queries_f32, uint32_t dim,
+                  const uint8_t* __restrict__ selector_bits, uint32_t selector_stride,
+                  const float* __restrict__ lut_outlier) {
     extern __shared__ unsigned long long pq2_keys[];
     float* sq = reinterpret_cast<float*>(pq2_keys + padded);   // [dim] query minus centroid (table-free form)
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -45,6 +47,7 @@ pq2_refine_kernel(const Cand* __restrict__ cand, const uint32_t* __restrict__ st
     for (uint64_t q = blockIdx.x; q < Q; q += gridDim.x) {
         const uint32_t valid = min(stats[q * 8 + 4], Lr);
         const float* lut = lut2 != nullptr ? lut2 + q * (uint64_t)M * kCentroids : nullptr;
+        const float* lut_out = lut_outlier != nullptr ? lut_outlier + q * (uint64_t)M * kCentroids : nullptr;
         if (lut == nullptr) {
             for (uint32_t i = threadIdx.x; i < dim; i += kPq2Threads) sq[i] = queries_f32[q * dim + i] - __ldg(mu2 + i);
             __syncthreads();
@@ -57,12 +60,16 @@ pq2_refine_kernel(const Cand* __restrict__ cand, const uint32_t* __restrict__ st
                 if (id != kInvalid) {
                     const uint8_t* rc_row = ShardRow(pq2_codes, id, M);
                     const uint8_t* bc_row = has_base ? ShardRow(base_codes, id, M) : nullptr;
+                    // hybrid PQ (src/search/rerank_exact.cu:667-771): bit m of the node's selector row picks the
+                    // outlier codebook's table for chunk m
+                    const uint8_t* sel_row = selector_bits != nullptr ? selector_bits + (uint64_t)id * selector_stride : nullptr;
                     float partial = 0.0f;
                     for (uint32_t m = lane; m < M; m += 32) {
                         const uint32_t rc = rc_row[m];
                         float entry;
                         if (lut != nullptr) {
-                            entry = lut[m * kCentroids + rc];
+                            const bool outlier = sel_row != nullptr && ((sel_row[m >> 3] >> (m & 7u)) & 1u) != 0;
+                            entry = (outlier ? lut_out : lut)[m * kCentroids + rc];
                         } else {
                             entry = 0.0f;
                             for (uint32_t k = __ldg(chunk_offsets + m); k < __ldg(chunk_offsets + m + 1); ++k) {
@@ -122,7 +129,8 @@ cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q,
                             const TannShards& pq2_codes, uint32_t M, const float* lut2,
                             const float* cross_terms, void* out, cudaStream_t stream,
                             const float* t2_col_major, const float* mu2, const uint32_t* chunk_offsets,
-                            const float* queries_f32, uint32_t dim) {
+                            const float* queries_f32, uint32_t dim, const uint8_t* selector_bits,
+                            uint32_t selector_stride, const float* lut_outlier) {
     if (Q == 0 || refine_top_l == 0) return cudaSuccess;
     uint32_t padded = 1;
     while (padded < refine_top_l) padded <<= 1;
@@ -137,7 +145,8 @@ cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q,
     pq2_refine_kernel<<<(unsigned)(Q < cap ? Q : cap), kPq2Threads, smem, stream>>>(
         static_cast<const Cand*>(cand), stats, Q, capacity, refine_top_l, padded,
         base_codes != nullptr ? 1 : 0, base_codes != nullptr ? *base_codes : none, pq2_codes, M, lut2,
-        cross_terms, static_cast<Cand*>(out), t2_col_major, mu2, chunk_offsets, queries_f32, dim);
+        cross_terms, static_cast<Cand*>(out), t2_col_major, mu2, chunk_offsets, queries_f32, dim, selector_bits,
+        selector_stride, lut_outlier);
     return cudaGetLastError();
 }
 

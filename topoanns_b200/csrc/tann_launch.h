@@ -38,7 +38,10 @@ cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q,
                             /* with lut2 == nullptr the table entries are computed from these instead */
                             const float* t2_col_major = nullptr, const float* mu2 = nullptr,
                             const uint32_t* chunk_offsets = nullptr, const float* queries_f32 = nullptr,
-                            uint32_t dim = 0);
+                            uint32_t dim = 0,
+                            /* hybrid PQ: bit m of a node's selector row picks lut_outlier for chunk m */
+                            const uint8_t* selector_bits = nullptr, uint32_t selector_stride = 0,
+                            const float* lut_outlier = nullptr);
 cudaError_t LaunchCrossTerms(uint32_t dim, uint32_t M, const uint32_t* chunk_offsets, const float* t1,
                              const float* mu1, const float* t2, const float* mu2, float* out,
                              cudaStream_t stream);

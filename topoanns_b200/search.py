@@ -270,6 +270,19 @@ def pq2_refine(cand, stats, refine_top_l, pq2_codes, lut2, base_codes=None, cros
     return out
 
 
+def hpq_refine(cand, stats, refine_top_l, hybrid_codes, selector_bits, base_lut, outlier_lut):
+    """Hybrid-PQ refine and re-sort (detail::RunHpqRefineBatchDevice, src/search/rerank_exact.cu:2457-2531):
+    hybrid_codes [N, M] uint8, selector_bits [N, (M + 7) // 8] uint8, the two query tables [Q, M, 256]."""
+    Q, capacity, _ = cand.shape
+    M = hybrid_codes.shape[1]
+    out = torch.empty((Q, refine_top_l, 2), dtype=torch.int32, device=cand.device)
+    codes = make_shards([hybrid_codes.data_ptr()])
+    capi.check(capi.load().tann_hpq_refine(_ptr(cand), _ptr(stats), Q, capacity, refine_top_l, C.byref(codes),
+                                           _ptr(selector_bits), M, _ptr(base_lut), _ptr(outlier_lut), _ptr(out), None,
+                                           _stream_ptr()))
+    return out
+
+
 def rerank_exact(index: DeviceIndex, params: RerankExactParams, cand: torch.Tensor, queries: torch.Tensor,
                  error_bounds: Optional[torch.Tensor] = None):
     """Returns (dists [Q, top_n] f32, ids [Q, top_n] int32, n_exact, n_filtered)."""
