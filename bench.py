@@ -317,8 +317,36 @@ def main():
         # every rank serves its own batch and reads its own results back: no data-path collective
         ids, dists, _ = sr.run_host(q_np, tp, rp, out_ids=out_ids_np, out_dists=out_dists_np)
     torch.cuda.synchronize()
+    e2e_serial_s = time.perf_counter() - t0
+    barrier()
+    # The same through two searchers on two streams, submitted alternately: batch i's copies overlap batch
+    # i-1's kernels. Every step still copies its queries in and its results out inside the timed region.
+    sr2 = search.Searcher(ix, Q, max_cap, max(TOPN_SWEEP), 128)
+    sr2.set_rvq(model, 128)
+    q2_np = torch.from_numpy(q_host).pin_memory().numpy()
+    out2_ids = torch.empty((Q, 10), dtype=torch.int32).pin_memory().numpy().view(np.uint32)
+    out2_dists = torch.empty((Q, 10), dtype=torch.float32).pin_memory().numpy()
+    lanes = [(sr, torch.cuda.Stream(device), q_np, out_ids_np, out_dists_np),
+             (sr2, torch.cuda.Stream(device), q2_np, out2_ids, out2_dists)]
+
+    def pipelined(steps):
+        for i in range(steps):
+            srx, st, qx, oi, od = lanes[i % 2]
+            srx.wait()
+            srx.submit_host(qx, tp, rp, oi, od, stream=st)
+        for srx, *_ in lanes:
+            srx.wait()
+
+    torch.cuda.synchronize()
+    pipelined(args.warmup)
+    barrier()
+    t0 = time.perf_counter()
+    pipelined(args.steps)
+    torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
+    assert np.array_equal(out2_ids, out_ids_np) and np.array_equal(out2_dists, out_dists_np)
+    sr2.close()
     clocks = sampler.stop() if rank == 0 else {}
     # ---- the beam-search kernel alone, for the roofline -----------------------------------------
     offs, eids, _ = model.device_entry_batch(q_dev, 128)
@@ -348,11 +376,11 @@ def main():
     smem, blocks_per_sm, grid = search.beam_occupancy(ix, tp, cap)
 
     # ---- max over ranks --------------------------------------------------------------------------
-    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms], dtype=torch.float64, device=device)
+    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms, e2e_serial_s * 1000.0], dtype=torch.float64, device=device)
     if world > 1:
         import torch.distributed as dist
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, beam_ms = [float(x) for x in times.cpu()]
+    dev_ms, e2e_ms, beam_ms, e2e_serial_ms = [float(x) for x in times.cpu()]
     if rank != 0:
         sr.close()
         if world > 1:
@@ -394,7 +422,9 @@ def main():
                                    "mean_visited": float(stats[:, 0].mean()),
                                    "bytes_per_query": beam_bytes / Q}},
         "e2e": {"value": total_q / (e2e_ms * 1e-3), "unit": "queries/s",
-                "h2d_bytes_per_step": int(q_host.nbytes), "d2h_bytes_per_step": int(Q * 10 * 8)},
+                "h2d_bytes_per_step": int(q_host.nbytes), "d2h_bytes_per_step": int(Q * 10 * 8),
+                "pipeline": "two searchers on two streams, batches submitted alternately (copies of one overlap kernels of the other)",
+                "one_batch_at_a_time": total_q / (e2e_serial_ms * 1e-3)},
         "gpu_launches": 5 * args.steps,  # rvq, beam, float->uint8 check, rerank, top-k pack
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -409,6 +409,18 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam,
                              const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
                              uint32_t* out_ids_host, float* out_dists_host,
                              uint32_t* out_stats_host, tann_stream_t stream);
+/* tann_searcher_run in two halves, for pipelining: submit enqueues the H2D copy, the kernels and the D2H copy
+ * on `stream` and returns without waiting; wait blocks until that batch's results are in the host buffers. Two
+ * searchers on two streams, submitted alternately, overlap one batch's copies with the other's kernels. One
+ * batch per searcher may be in flight; host buffers must stay valid until wait returns. An early return of
+ * submit (Q == 0 or an error) leaves nothing pending. */
+TannStatus tann_searcher_submit(TannSearcher* s, const TannBeamParams* beam,
+                                const TannRerankParams* rerank, const void* queries_host,
+                                uint32_t query_kind, uint64_t num_queries,
+                                const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
+                                uint32_t* out_ids_host, float* out_dists_host,
+                                uint32_t* out_stats_host, tann_stream_t stream);
+TannStatus tann_searcher_wait(TannSearcher* s);
 /* Same, device buffers in and out, nothing copied; results stay in the searcher's buffers until
  * the next call. Pointers returned through out_* are device pointers owned by the searcher. */
 TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,

@@ -447,6 +447,47 @@ def test_rvq_clusters_agree_with_gemm_scores():
         assert min(gap0, gap1) < 1e-4, (i, gap0, gap1)
 
 
+def test_pipelined_searchers_give_the_results_of_single_calls():
+    """tann_searcher_submit / tann_searcher_wait: two searchers on two streams, batches submitted alternately,
+    page-locked and pageable buffers; every batch equals the blocking call's answer."""
+    s, host = small_index(name="cfg2", num_nodes=40000, components=40, num_queries=300)
+    ix = device_index(s)
+    model = search.rvq_model_from_synth(s)
+    lanes = []
+    for _ in range(2):
+        sr = search.Searcher(ix, 512, 128, 64, 128)
+        sr.set_rvq(model, 128)
+        lanes.append((sr, torch.cuda.Stream()))
+    tp = search.TopologySearchParams(top_l=32, search_width=2, max_expansions=4096)
+    rp = search.RerankExactParams(top_k=10, top_n=32)
+    q = s.queries.cpu().numpy()
+    batches = [np.ascontiguousarray(q[i * 50:(i + 1) * 50 + 17]) for i in range(5)]
+    want = [lanes[0][0].run_host(b, tp, rp)[:2] for b in batches]
+    pinned = [torch.from_numpy(b).pin_memory().numpy() for b in batches]
+    outs = []
+    for i, b in enumerate(batches):
+        n = b.shape[0]
+        if i % 2 == 0:   # page-locked in and out
+            oi = torch.empty((n, 10), dtype=torch.int32).pin_memory().numpy().view(np.uint32)
+            od = torch.empty((n, 10), dtype=torch.float32).pin_memory().numpy()
+            src = pinned[i]
+        else:            # pageable: staged inside the searcher
+            oi, od, src = np.empty((n, 10), np.uint32), np.empty((n, 10), np.float32), b
+        outs.append((oi, od))
+        sr, st = lanes[i % 2]
+        sr.wait()
+        sr.submit_host(src, tp, rp, oi, od, stream=st)
+    with pytest.raises(capi.TannError, match="has not been waited for"):
+        lanes[0][0].submit_host(batches[0], tp, rp, *outs[0], stream=lanes[0][1])
+    for sr, _ in lanes:
+        sr.wait()
+        sr.wait()   # nothing pending: no-op
+    for (oi, od), (wi, wd) in zip(outs, want):
+        assert np.array_equal(oi, wi) and np.array_equal(od.view(np.uint32), wd.view(np.uint32))
+    for sr, _ in lanes:
+        sr.close()
+
+
 def test_full_pipeline_matches_checker_with_rvq():
     s, host = small_index(name="cfg2", num_nodes=40000, components=40, num_queries=300)
     ix = device_index(s)

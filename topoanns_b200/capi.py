@@ -135,6 +135,9 @@ SIGNATURES = {
     "tann_searcher_set_pq2": (_I, [_VP, C.POINTER(Pq2View)]),
     "tann_searcher_run": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64, _VP,
                                _U32, _VP, _VP, _VP, _VP]),
+    "tann_searcher_submit": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64, _VP,
+                                  _U32, _VP, _VP, _VP, _VP]),
+    "tann_searcher_wait": (_I, [_VP]),
     "tann_searcher_run_device": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64,
                                       _VP, _VP, C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP), _VP]),
     "tann_searcher_destroy": (_I, [_VP]),

@@ -605,6 +605,15 @@ struct TannSearcher {
     uint32_t* d_topk_ids;
     unsigned long long* d_counts;
     // pinned staging
+    // a batch that tann_searcher_submit enqueued and tann_searcher_wait has not collected yet
+    struct Pending {
+        bool active = false;
+        cudaStream_t stream = nullptr;
+        uint32_t* out_ids = nullptr;     // non-null: copy from the staging buffer after the stream drains
+        float* out_dists = nullptr;
+        uint32_t* out_stats = nullptr;
+        size_t kbytes = 0, stats_bytes = 0;
+    } pending;
     void* h_queries;
     uint32_t* h_topk_ids;
     float* h_topk_dists;
@@ -786,14 +795,15 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
     return TANN_OK;
 }
 
-TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const TannRerankParams* rerank,
-                             const void* queries_host, uint32_t query_kind, uint64_t Q,
-                             const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
-                             uint32_t* out_ids_host, float* out_dists_host, uint32_t* out_stats_host,
-                             tann_stream_t stream_) {
+TannStatus tann_searcher_submit(TannSearcher* s, const TannBeamParams* beam, const TannRerankParams* rerank,
+                                const void* queries_host, uint32_t query_kind, uint64_t Q,
+                                const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
+                                uint32_t* out_ids_host, float* out_dists_host, uint32_t* out_stats_host,
+                                tann_stream_t stream_) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!s || !beam || !rerank || !queries_host || !out_ids_host || !out_dists_host)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: null pointer.");
+    if (s->pending.active) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_submit: the previous batch has not been waited for.");
     if (Q > s->max_queries) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: batch exceeds max_queries.");
     if (query_kind > TANN_KIND_FLOAT32) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: unknown query kind.");
     if (Q == 0) return TANN_OK;
@@ -831,11 +841,39 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const 
     TANN_CUDA(cudaMemcpyAsync(dists_direct ? (void*)out_dists_host : (void*)s->h_topk_dists, s->d_topk_dists, kbytes,
                               cudaMemcpyDeviceToHost, stream));
     if (out_stats_host) TANN_CUDA(cudaMemcpyAsync(s->h_stats, s->d_stats, Q * 32, cudaMemcpyDeviceToHost, stream));
-    TANN_CUDA(cudaStreamSynchronize(stream));
-    if (!ids_direct) memcpy(out_ids_host, s->h_topk_ids, kbytes);
-    if (!dists_direct) memcpy(out_dists_host, s->h_topk_dists, kbytes);
-    if (out_stats_host) memcpy(out_stats_host, s->h_stats, Q * 32);
+    s->pending.active = true;
+    s->pending.stream = stream;
+    s->pending.out_ids = ids_direct ? nullptr : out_ids_host;
+    s->pending.out_dists = dists_direct ? nullptr : out_dists_host;
+    s->pending.out_stats = out_stats_host;
+    s->pending.kbytes = kbytes;
+    s->pending.stats_bytes = Q * 32;
     return TANN_OK;
+}
+
+TannStatus tann_searcher_wait(TannSearcher* s) {
+    if (!s) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_wait: null searcher.");
+    if (!s->pending.active) return TANN_OK;
+    s->pending.active = false;
+    TANN_CUDA(cudaStreamSynchronize(s->pending.stream));
+    if (s->pending.out_ids) memcpy(s->pending.out_ids, s->h_topk_ids, s->pending.kbytes);
+    if (s->pending.out_dists) memcpy(s->pending.out_dists, s->h_topk_dists, s->pending.kbytes);
+    if (s->pending.out_stats) memcpy(s->pending.out_stats, s->h_stats, s->pending.stats_bytes);
+    return TANN_OK;
+}
+
+TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const TannRerankParams* rerank,
+                             const void* queries_host, uint32_t query_kind, uint64_t Q,
+                             const uint32_t* fixed_entries_host, uint32_t num_fixed_entries,
+                             uint32_t* out_ids_host, float* out_dists_host, uint32_t* out_stats_host,
+                             tann_stream_t stream) {
+    const TannStatus st = tann_searcher_submit(s, beam, rerank, queries_host, query_kind, Q, fixed_entries_host,
+                                               num_fixed_entries, out_ids_host, out_dists_host, out_stats_host, stream);
+    if (st != TANN_OK) {
+        if (s) s->pending.active = false;
+        return st;
+    }
+    return tann_searcher_wait(s);
 }
 
 TannStatus tann_searcher_destroy(TannSearcher* s) {

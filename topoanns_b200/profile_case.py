@@ -11,7 +11,7 @@ import dataclasses
 
 import torch
 
-from . import search, synth
+from . import capi, search, synth
 
 
 def _time(fn, reps):
@@ -119,6 +119,22 @@ def main() -> None:
         rp2 = search.RerankExactParams(top_k=10, top_n=min(a.top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
         (_, _, n_exact, n_flt), ms = _time(lambda: search.rerank_exact(ix, rp2, refined, q, eps), a.reps)
         print(f"rerank_exact (tiled, bound filter) {ms:.3f} ms  exact={n_exact} filtered={n_flt}")
+        # persistent rerank with a learned stop: a synthetic model on the share of ranks scored and the top-k
+        # churn (logit = 1 - 2.5 * prefix / budget + entered / k, threshold 0)
+        ls = capi.RerankLearnedStop()
+        budget = rp2.top_n
+        stages = [pfx for pfx in (16, 32, 48, 64, 96, 128, 192, 256, 384, 512) if pfx < budget]
+        ls.enabled, ls.num_stages, ls.top_k, ls.bootstrap_prefix = 1, len(stages), 10, 16
+        for i, pfx in enumerate(stages):
+            ls.stage_prefixes[i] = pfx
+        while ls.initial_stage_index < ls.num_stages and ls.stage_prefixes[ls.initial_stage_index] <= 16:
+            ls.initial_stage_index += 1
+        ls.linear_weights[1], ls.linear_weights[6], ls.bias, ls.threshold_logit = -2.5, 1.0, 1.0, 0.0
+        ls.inv_budget_top_n, ls.inv_top_k = 1.0 / budget, 0.1
+        if ls.initial_stage_index < ls.num_stages:
+            res, ms = _time(lambda: search.rerank_exact_learned_stop(ix, rp2, refined, q, model=ls, error_bounds=eps), a.reps)
+            print(f"rerank_exact_learned_stop {ms:.3f} ms  exact={res['n_exact']} filtered={res['n_filtered']} "
+                  f"mean_stop_prefix={float(res['stop_prefixes'].float().mean()):.1f} of {budget}")
         if cfg.rvq:
             sr = search.Searcher(ix, a.queries, cap, min(a.top_n, lr), a.entries)
             sr.set_rvq(model, a.entries)

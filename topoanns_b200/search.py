@@ -406,6 +406,28 @@ class Searcher:
             stats.ctypes.data_as(C.c_void_p) if stats is not None else None, _stream_ptr()))
         return ids, dists, stats
 
+    def submit_host(self, queries: np.ndarray, topology: TopologySearchParams, rerank: RerankExactParams,
+                    out_ids: np.ndarray, out_dists: np.ndarray, stream: Optional[torch.cuda.Stream] = None):
+        """First half of run_host: enqueues copy-in, kernels and copy-out on `stream` (default: the current
+        stream) and returns at once; wait() completes the batch. Two searchers submitted alternately on two
+        streams overlap one batch's copies with the other's kernels. The arrays must stay alive until wait()."""
+        q = queries
+        assert q.flags.c_contiguous and out_ids.flags.c_contiguous and out_dists.flags.c_contiguous
+        Q = q.shape[0]
+        assert out_ids.shape == (Q, rerank.top_k) and out_ids.dtype == np.uint32
+        assert out_dists.shape == (Q, rerank.top_k) and out_dists.dtype == np.float32
+        bp = topology.to_c(topology.capacity(rerank.top_n))
+        rp = rerank.to_c()
+        sp = C.c_void_p(stream.cuda_stream) if stream is not None else _stream_ptr()
+        self._in_flight = (q, out_ids, out_dists)
+        capi.check(capi.load().tann_searcher_submit(
+            self._h, C.byref(bp), C.byref(rp), q.ctypes.data_as(C.c_void_p), _NP_KIND[str(q.dtype)], Q, None, 0,
+            out_ids.ctypes.data_as(C.c_void_p), out_dists.ctypes.data_as(C.c_void_p), None, sp))
+
+    def wait(self):
+        capi.check(capi.load().tann_searcher_wait(self._h))
+        self._in_flight = None
+
     def run_device(self, queries: torch.Tensor, topology: TopologySearchParams, rerank: RerankExactParams,
                    entry_offsets: Optional[torch.Tensor] = None, entry_ids: Optional[torch.Tensor] = None):
         """Device queries in; returns raw device pointers (ids, dists, stats) owned by the searcher."""
