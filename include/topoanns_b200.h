@@ -401,6 +401,9 @@ TannStatus tann_searcher_create(const TannIndexView* index, uint64_t max_queries
                                 uint32_t max_entries_per_query, TannSearcher** out);
 TannStatus tann_searcher_set_rvq(TannSearcher* s, const TannRvqModelView* rvq);
 TannStatus tann_searcher_set_pq2(TannSearcher* s, const TannPq2View* pq2);
+/* Reranks of this searcher run the persistent rerank with this learned-stop model (folded for the top_n the
+ * runs will use, see tann_rerank_learned_stop_load); NULL switches back to the plain rerank. */
+TannStatus tann_searcher_set_rerank_learned_stop(TannSearcher* s, const TannRerankLearnedStop* model);
 /* queries_host: [Q][dim] of query_kind. fixed_entries_host may be NULL when an RVQ model is set.
  * out_ids_host / out_dists_host: [Q][top_k]. out_stats_host: [Q][8] or NULL. */
 TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam,

@@ -274,3 +274,32 @@ def test_learned_stop_float_index_with_bound_filter(tmp_path, model_text, thresh
     rp = search.RerankExactParams(top_k=10, top_n=128, rank_tile_size=16)
     with pytest.raises(RuntimeError, match="next-window features"):
         search.rerank_exact_learned_stop(ix, rp, refined, q, model=model)
+
+
+@pytest.mark.gpu
+def test_searcher_with_learned_stop_equals_the_staged_calls(tmp_path):
+    """tann_searcher_set_rerank_learned_stop: the whole path with the learned stop gives what beam search +
+    tann_rerank_exact_learned_stop give when called one after the other."""
+    torch, capi, search, gs = _gpu_imports()
+    s, host = gs.small_index()
+    ix = gs.device_index(s)
+    Q = s.queries.shape[0]
+    top_n = 128
+    tp = search.TopologySearchParams(top_l=top_n, search_width=2, max_expansions=4096)
+    rp = search.RerankExactParams(top_k=10, top_n=top_n, rank_tile_size=16)
+    q = s.queries.cuda().contiguous()
+    eo, ei = gs.fixed_entries(Q, [s.medoid])
+    cand, _ = search.beam_search(ix, tp, eo, ei, queries=q, capacity=tp.capacity(top_n))
+    model = search.load_rerank_learned_stop(_write(tmp_path, "m", MODEL_NO_NEXT_WINDOW.format(threshold=0.1)), top_n, 10)
+    want = search.rerank_exact_learned_stop(ix, rp, cand, q, model=model)
+    sr = search.Searcher(ix, Q, tp.capacity(top_n), top_n, 4)
+    sr.set_rerank_learned_stop(model)
+    ids, dists, _ = sr.run_host(s.queries.cpu().numpy(), tp, rp, fixed_entries=np.array([s.medoid], np.uint32))
+    assert np.array_equal(ids, gs.np_u32(want["ids"]))
+    assert np.array_equal(dists.view(np.uint32), want["dists"].cpu().numpy().view(np.uint32))
+    sr.set_rerank_learned_stop(None)
+    ids2, _, _ = sr.run_host(s.queries.cpu().numpy(), tp, rp, fixed_entries=np.array([s.medoid], np.uint32))
+    d_full, i_full, _, _ = search.rerank_exact(ix, rp, cand, q)
+    assert np.array_equal(ids2, gs.np_u32(i_full[:, :10]))
+    assert int(want["stop_prefixes"].float().mean()) < top_n
+    sr.close()

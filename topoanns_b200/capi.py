@@ -135,6 +135,7 @@ SIGNATURES = {
     "tann_searcher_set_pq2": (_I, [_VP, C.POINTER(Pq2View)]),
     "tann_searcher_run": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64, _VP,
                                _U32, _VP, _VP, _VP, _VP]),
+    "tann_searcher_set_rerank_learned_stop": (_I, [_VP, C.POINTER(RerankLearnedStop)]),
     "tann_searcher_submit": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64, _VP,
                                   _U32, _VP, _VP, _VP, _VP]),
     "tann_searcher_wait": (_I, [_VP]),

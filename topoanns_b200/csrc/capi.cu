@@ -586,6 +586,8 @@ struct TannSearcher {
     uint64_t max_queries;
     uint32_t max_capacity, max_top_n, max_entries;
     bool has_rvq, has_pq2;
+    bool has_rerank_stop = false;
+    TannRerankLearnedStop rerank_stop;
     TannRvqModelView rvq;
     TannPq2View pq2;
     // device work space
@@ -700,6 +702,13 @@ TannStatus tann_searcher_set_pq2(TannSearcher* s, const TannPq2View* pq2) {
     return TANN_OK;
 }
 
+TannStatus tann_searcher_set_rerank_learned_stop(TannSearcher* s, const TannRerankLearnedStop* model) {
+    if (!s) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_set_rerank_learned_stop: null searcher.");
+    s->has_rerank_stop = model != nullptr;
+    if (model) s->rerank_stop = *model;
+    return TANN_OK;
+}
+
 __global__ void to_float_kernel(const void* src, uint32_t kind, uint64_t n, float* dst) {
     for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         dst[i] = kind == TANN_KIND_UINT8 ? (float)static_cast<const uint8_t*>(src)[i]
@@ -773,6 +782,17 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         cand = s->d_cand_refined;
         capacity = lr;
         err = p2.error_bounds;
+    }
+    if (s->has_rerank_stop && rerank->top_n != 0) {
+        // persistent rerank with the learned stop: keeps the top_k list itself, nothing to pack
+        st = tann_rerank_exact_learned_stop(&s->ix, rerank, &s->rerank_stop, cand, capacity, Q, queries_dev, query_kind, err,
+                                            nullptr, s->d_topk_dists, s->d_topk_ids, nullptr, nullptr, nullptr, nullptr,
+                                            nullptr, stream);
+        if (st != TANN_OK) return st;
+        if (out_ids_dev) *out_ids_dev = s->d_topk_ids;
+        if (out_dists_dev) *out_dists_dev = s->d_topk_dists;
+        if (out_stats_dev) *out_stats_dev = s->d_stats;
+        return TANN_OK;
     }
     if (rerank->top_n != 0) {
         st = CheckRerank(&s->ix, rerank, err);

@@ -406,6 +406,11 @@ class Searcher:
             stats.ctypes.data_as(C.c_void_p) if stats is not None else None, _stream_ptr()))
         return ids, dists, stats
 
+    def set_rerank_learned_stop(self, model: Optional[capi.RerankLearnedStop]):
+        """Reranks of this searcher use the persistent rerank with this learned-stop model (None: plain rerank)."""
+        capi.check(capi.load().tann_searcher_set_rerank_learned_stop(
+            self._h, C.byref(model) if model is not None else None))
+
     def submit_host(self, queries: np.ndarray, topology: TopologySearchParams, rerank: RerankExactParams,
                     out_ids: np.ndarray, out_dists: np.ndarray, stream: Optional[torch.cuda.Stream] = None):
         """First half of run_host: enqueues copy-in, kernels and copy-out on `stream` (default: the current
