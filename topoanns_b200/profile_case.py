@@ -58,7 +58,6 @@ def main() -> None:
     if a.topology == "pinned-host":
         import ctypes as C
 
-        from . import capi
         lib = capi.load()
         nbytes = ix.adjacency.numel() * 4
         hp, dp = C.c_void_p(), C.c_void_p()
