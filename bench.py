@@ -58,6 +58,8 @@ def parse_args():
     ap.add_argument("--top-n", type=int, default=0, help="with --top-l: rerank top_n (default 32)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streams", type=int, default=4,
+                    help="searchers (each on its own stream) that the steps alternate between; 1 = one batch at a time")
     ap.add_argument("--no-neighbor-codes", action="store_true",
                     help="do not build the neighbour-code layout (degree * M bytes per node of extra HBM)")
     ap.add_argument("--sharded", action="store_true",
@@ -306,25 +308,32 @@ def main():
     # The same K steps through two searchers on two streams, submitted alternately: the short kernels of one batch
     # (entry selection, rerank, top-k) and the ragged last wave of its beam search run beside the other batch's
     # beam search. Timed with events: both streams start after ev0, ev1 follows the end of both.
-    sr2 = search.Searcher(ix, Q, max_cap, max(TOPN_SWEEP), 128)
-    sr2.set_rvq(model, 128)
-    q_dev2 = q_dev.clone()
-    stream_a, stream_b = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    n_lanes = max(1, args.streams)
+    searchers, streams, q_devs = [sr], [torch.cuda.Stream(device)], [q_dev]
+    for _ in range(n_lanes - 1):
+        extra = search.Searcher(ix, Q, max_cap, max(TOPN_SWEEP), 128)
+        extra.set_rvq(model, 128)
+        searchers.append(extra)
+        streams.append(torch.cuda.Stream(device))
+        q_devs.append(q_dev.clone())
 
-    def two_streams(steps):
+    def many_streams(steps):
         for i in range(steps):
-            with torch.cuda.stream(stream_a if i % 2 == 0 else stream_b):
-                (sr if i % 2 == 0 else sr2).run_device(q_dev if i % 2 == 0 else q_dev2, tp, rp)
+            with torch.cuda.stream(streams[i % n_lanes]):
+                searchers[i % n_lanes].run_device(q_devs[i % n_lanes], tp, rp)
 
-    two_streams(max(args.warmup, 2))
+    many_streams(max(args.warmup, n_lanes))
     barrier()
-    ev0, ev1, ev_b = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-    ev0.record(stream_a)
-    stream_b.wait_event(ev0)
-    two_streams(args.steps)
-    ev_b.record(stream_b)
-    stream_a.wait_event(ev_b)
-    ev1.record(stream_a)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(streams[0])
+    for st in streams[1:]:
+        st.wait_event(ev0)
+    many_streams(args.steps)
+    for st in streams[1:]:
+        done = torch.cuda.Event()
+        done.record(st)
+        streams[0].wait_event(done)
+    ev1.record(streams[0])
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
     # ---- host-buffer leg: `e2e` ----------------------------------------------------------------
@@ -345,14 +354,15 @@ def main():
     barrier()
     # The same through two searchers on two streams, submitted alternately: batch i's copies overlap batch
     # i-1's kernels. Every step still copies its queries in and its results out inside the timed region.
-    q2_np = torch.from_numpy(q_host).pin_memory().numpy()
-    out2_ids = torch.empty((Q, 10), dtype=torch.int32).pin_memory().numpy().view(np.uint32)
-    out2_dists = torch.empty((Q, 10), dtype=torch.float32).pin_memory().numpy()
-    lanes = [(sr, stream_a, q_np, out_ids_np, out_dists_np), (sr2, stream_b, q2_np, out2_ids, out2_dists)]
+    lanes = [(sr, streams[0], q_np, out_ids_np, out_dists_np)]
+    for k in range(1, n_lanes):
+        lanes.append((searchers[k], streams[k], torch.from_numpy(q_host).pin_memory().numpy(),
+                      torch.empty((Q, 10), dtype=torch.int32).pin_memory().numpy().view(np.uint32),
+                      torch.empty((Q, 10), dtype=torch.float32).pin_memory().numpy()))
 
     def pipelined(steps):
         for i in range(steps):
-            srx, st, qx, oi, od = lanes[i % 2]
+            srx, st, qx, oi, od = lanes[i % n_lanes]
             srx.wait()
             srx.submit_host(qx, tp, rp, oi, od, stream=st)
         for srx, *_ in lanes:
@@ -366,8 +376,10 @@ def main():
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
-    assert np.array_equal(out2_ids, out_ids_np) and np.array_equal(out2_dists, out_dists_np)
-    sr2.close()
+    for _, _, _, oi, od in lanes[1:]:
+        assert np.array_equal(oi, out_ids_np) and np.array_equal(od, out_dists_np)
+    for extra in searchers[1:]:
+        extra.close()
     clocks = sampler.stop() if rank == 0 else {}
     # ---- the beam-search kernel alone, for the roofline -----------------------------------------
     offs, eids, _ = model.device_entry_batch(q_dev, 128)
@@ -435,7 +447,7 @@ def main():
                    "parallelism": (f"node-id-range shards x{world}, queries sharded" if sharded
                                    else f"replica x{world}, queries sharded"),
                    "l2_policy": "index (4.2 GB) and per-step gathers exceed the 126 MB L2; no flush",
-                   "streams": "2: steps alternate between two searchers on two streams; one stream alone: "
+                   "streams": f"{n_lanes}: steps alternate between {n_lanes} searchers, each on its own stream; one stream alone: "
                               f"{total_q / (dev_one_stream_ms * 1e-3):.0f} queries/s, {dev_one_stream_ms / args.steps:.4f} ms per step",
                    "layout": ("adjacency + PQ codes + vector pages in HBM"
                               + (f" + neighbour codes next to each node ({ix.neighbor_codes.numel() / 1e9:.1f} GB)"
@@ -447,7 +459,7 @@ def main():
                                    "bytes_per_query": beam_bytes / Q}},
         "e2e": {"value": total_q / (e2e_ms * 1e-3), "unit": "queries/s",
                 "h2d_bytes_per_step": int(q_host.nbytes), "d2h_bytes_per_step": int(Q * 10 * 8),
-                "pipeline": "two searchers on two streams, batches submitted alternately (copies of one overlap kernels of the other)",
+                "pipeline": f"{n_lanes} searchers on {n_lanes} streams, batches submitted in turn (copies of one overlap kernels of the others)",
                 "one_batch_at_a_time": total_q / (e2e_serial_ms * 1e-3)},
         "gpu_launches": 5 * args.steps,  # rvq, beam, float->uint8 check, rerank, top-k pack
         "clocks": clocks,
