@@ -897,6 +897,10 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const 
 }
 
 TannStatus tann_searcher_destroy(TannSearcher* s) {
+    if (s && s->pending.active) {   // a submitted batch still uses the buffers: let it drain first
+        cudaStreamSynchronize(s->pending.stream);
+        s->pending.active = false;
+    }
     FreeSearcher(s);
     return TANN_OK;
 }
