@@ -772,7 +772,7 @@ cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams&
                                              (int)smem);
         if (e != cudaSuccess) return e;
     }
-    const uint64_t cap = (uint64_t)SmCount() * 8;
+    const uint64_t cap = (uint64_t)SmCount() * 9;   // 56 registers: nine blocks per SM are resident
     rerank_learned_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, model, use_schedule ? 1u : 0u, evaluate ? 1u : 0u, static_cast<const Cand*>(cand), capacity, Q, queries,
         query_kind, error_bounds, replay_stop_prefixes, padded, out_dists, out_ids, out_counts, out_stop_prefixes,
