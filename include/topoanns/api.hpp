@@ -12,8 +12,10 @@
 //     pinned-host pages) instead of a BaM array; the three providers are declared below and replace
 //     BamVectorPageProvider.
 //   * topology.bin files of any degree load (the reference accepts 64 only).
-//   * RerankExecutionMode::kPersistent runs the same fused tile kernel as kTiled; early / learned
-//     rerank stops are rejected with an error.
+//   * RerankExecutionMode::kPersistent runs the same fused tile kernel as kTiled; the rerank early stop
+//     works in the tiled and persistent modes, and the learned rerank stop (persistent mode + bound
+//     filter, as in the reference) runs on every vector provider and scalar kind, not only on the
+//     NVMe provider with float32 vectors.
 #pragma once
 
 #include <cuda_runtime.h>

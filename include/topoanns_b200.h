@@ -32,6 +32,15 @@ typedef enum TannStatus {
     TANN_ERR_DEVICE_CHECK = 4      /* a kernel recorded an out-of-range index (status word) */
 } TannStatus;
 
+/* Bits a kernel ors into the caller's device status word (the `status` arguments below; the searcher keeps its
+ * own word and turns a non-zero value into TANN_ERR_DEVICE_CHECK). The check always precedes the access: the
+ * offending id is skipped, exactly as the reference skips it (src/search/topology_search_kernel.cu:2556-2559,
+ * src/search/rerank_exact.cu:344-386), and the results are those of the remaining ids. */
+#define TANN_STATUS_BEAM_ID_RANGE 1u     /* an entry or adjacency id that is neither 0xffffffff nor < num_nodes */
+#define TANN_STATUS_RERANK_ID_RANGE 2u   /* a candidate id >= num_nodes reached the rerank */
+#define TANN_STATUS_COPY_TIMEOUT 4u      /* a bulk shared-memory copy did not complete within its poll limit; the
+                                            block wrote no results for its remaining queries */
+
 /* include/topoanns/common.hpp:17-21 (ScalarKind) */
 enum { TANN_KIND_INT8 = 0, TANN_KIND_UINT8 = 1, TANN_KIND_FLOAT32 = 2 };
 
@@ -145,7 +154,9 @@ TannStatus tann_lut_build(const float* tables_col_major /*dev [dim][256]*/,
  *             `queries` (then queries / query_kind must be given);
  *   entries   CSR as in DeviceEntryBatch (include/topoanns/device_entry_batch.hpp:10-23);
  *   out_candidates dev [Q][candidate_capacity] records, out_stats dev [Q][8] uint32;
- *   status    dev uint32, set non-zero if a kernel met an index outside the index view (optional).
+ *   status    dev uint32 or NULL; TANN_STATUS_* bits are or-ed into it (clear it before the call).
+ * Alignment: `lut`, every base pointer of `index->codes` and of `index->neighbor_codes`, and the PQ pivots must
+ * be 16-byte aligned (rows are read with 16-byte loads); anything else is rejected before the launch.
  */
 TannStatus tann_beam_search(const TannIndexView* index, const TannBeamParams* params,
                             const float* lut /*dev or NULL*/, const void* queries /*dev or NULL*/,
@@ -189,7 +200,8 @@ TannStatus tann_rvq_entries(const float* queries /*dev [Q][dim]*/, uint64_t num_
  * pq2 refine and re-sort of the first refine_top_l candidates of every query. Replaces
  * RunPq2RefineBatchDevice (src/search/rerank_exact.cu:2263-2455; kernels :573-665 plain,
  * :773-879 residual). base_codes == NULL selects the plain form. Output: dev
- * [Q][refine_top_l] records sorted by (distance, id), expanded flags cleared.
+ * [Q][refine_top_l] records sorted by (distance, id), expanded flags cleared. `status` is accepted for
+ * symmetry and not written: the ids come out of tann_beam_search, which has range-checked them.
  */
 TannStatus tann_pq2_refine(const void* candidates /*dev [Q][capacity]*/,
                            const uint32_t* stats /*dev [Q][8]*/, uint64_t num_queries,
@@ -247,7 +259,8 @@ typedef struct TannRerankParams {
  * uint8 vectors are computed in integers (dp4a) and converted once; every other pair of kinds
  * uses the reference's float order (lane-strided FMA partials + shuffle tree).
  *   out_dists / out_ids dev [Q][top_n] sorted, skipped or invalid ranks = (+inf, 0xffffffff);
- *   out_counts dev uint64[2] += { exact distances computed, candidates filtered } (optional).
+ *   out_counts dev uint64[2] += { exact distances computed, candidates filtered } (optional);
+ *   status dev uint32 or NULL: TANN_STATUS_RERANK_ID_RANGE is or-ed in when a candidate id >= num_nodes is skipped.
  */
 TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams* params,
                              const void* candidates /*dev [Q][capacity]*/, uint32_t capacity,
@@ -433,6 +446,17 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
                                     const uint32_t** out_ids_dev, const float** out_dists_dev,
                                     const uint32_t** out_stats_dev, tann_stream_t stream);
 TannStatus tann_searcher_destroy(TannSearcher* s);
+/* The searcher's device status word (TANN_STATUS_* bits of its last run; cleared when a run starts).
+ * tann_searcher_wait / tann_searcher_run read it back and return TANN_ERR_DEVICE_CHECK when it is non-zero (the
+ * results are still delivered); callers of tann_searcher_run_device read it themselves. */
+TannStatus tann_searcher_status_device(TannSearcher* s, const uint32_t** out_status_dev);
+
+/* Mean time in nanoseconds of one dependent random 4-byte load out of `bytes` bytes of device memory at `base`
+ * (one thread chasing `steps` loads, each address derived from the value just read): the memory round trip that
+ * one expansion of the beam search cannot go below. A measurement aid for reports; synchronises `stream`.
+ * No counterpart in the reference. */
+TannStatus tann_dependent_load_ns(const void* base /*dev*/, uint64_t bytes, uint32_t steps, float* out_ns /*host*/,
+                                  tann_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -6,7 +6,11 @@
 # The reference's build system is not used (it needs a BaM submodule that is not vendored).
 #   usage: ref_build.sh /path/to/reference
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${TOPOANNS_REFERENCE:-}}"
+if [[ -z "$REF" || ! -d "$REF" ]]; then
+    echo "usage: ref_build.sh /path/to/reference (or set TOPOANNS_REFERENCE)" >&2
+    exit 2
+fi
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
 mkdir -p "$OUT/obj"

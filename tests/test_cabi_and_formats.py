@@ -60,6 +60,29 @@ def test_parameter_checks_answer_without_a_gpu():
     assert b"error bounds" in lib.tann_last_error()
 
 
+def test_misaligned_tables_and_code_rows_are_rejected_before_any_launch():
+    """Query tables, PQ code rows and neighbour-code rows are read with 16-byte loads: a base pointer off a
+    16-byte boundary is answered with an error status on the host, nothing is launched."""
+    lib = capi.load()
+    v, p = capi.IndexView(), capi.BeamParams()
+    p.top_l, p.search_width, p.max_expansions, p.candidate_capacity = 8, 2, 16, 8
+    v.num_nodes, v.degree, v.num_chunks, v.dim = 100, 32, 32, 128
+    v.adjacency.num_shards = v.codes.num_shards = 1
+    v.adjacency.base[0] = 4096
+    v.codes.base[0] = 8192
+    args = (0, 4, 4096, 4096, 4096, 4096, None, None)     # kind, Q, offsets, ids, out, stats, status, stream
+    assert lib.tann_beam_search(C.byref(v), C.byref(p), 4096 + 4, None, *args) == 1      # table at base + 4 bytes
+    assert b"query tables must be 16-byte aligned" in lib.tann_last_error()
+    v.codes.base[0] = 8192 + 4
+    assert lib.tann_beam_search(C.byref(v), C.byref(p), 4096, None, *args) == 1
+    assert b"codes shard 0 must be 16-byte aligned" in lib.tann_last_error()
+    v.codes.base[0] = 8192
+    v.neighbor_codes.num_shards = 1
+    v.neighbor_codes.base[0] = 16384 + 8
+    assert lib.tann_beam_search(C.byref(v), C.byref(p), 4096, None, *args) == 1
+    assert b"neighbor_codes shard 0 must be 16-byte aligned" in lib.tann_last_error()
+
+
 def test_capacity_rule():
     # nextpow2(max(top_l, candidate_queue_size, rerank top_n))
     assert capi.candidate_capacity(4, 0, 5) == 8

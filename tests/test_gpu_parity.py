@@ -190,7 +190,12 @@ def test_ragged_invalid_and_empty_entries():
     ids = np.array([x for l in lists for x in l], np.uint32)
     eo, ei = _dev(offsets), _dev(ids)
     p = search.TopologySearchParams(top_l=32, search_width=2, max_expansions=512)
-    cand, stats = search.beam_search(ix, p, eo, ei, queries=q)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cand, stats = search.beam_search(ix, p, eo, ei, queries=q, status=status)
+    assert int(status.item()) == 1      # TANN_STATUS_BEAM_ID_RANGE: the id beyond the index was skipped and reported
+    clean = torch.zeros(1, dtype=torch.int32, device="cuda")
+    search.beam_search(ix, p, eo[:2].contiguous(), ei[:1].contiguous(), queries=q[:1].contiguous(), status=clean)
+    assert int(clean.item()) == 0
     lut_ref = orc.lut_build(s.queries[:Q].cpu().numpy(), host["pq_tables"], host["pq_centroid"], host["pq_chunk_offsets"])
     ref_cand, ref_stats = orc.beam_search(host["adjacency"], host["codes"], lut_ref, offsets, ids, top_l=32,
                                           search_width=2, max_expansions=512)
@@ -506,6 +511,27 @@ def test_full_pipeline_matches_checker_with_rvq():
         # uint8 queries through the same call give the same answer (integer rerank path)
         ids8, dists8, _ = sr.run_host(s.queries.cpu().numpy().astype(np.uint8), tp, rp)
         assert np.array_equal(ids8, ids) and np.array_equal(dists8, dists)
+    sr.close()
+
+
+def test_searcher_reports_an_entry_id_outside_the_index():
+    """A fixed entry list with an id beyond the index: the id is skipped as the reference skips it (the results are
+    those of the valid entries) and the call answers TANN_ERR_DEVICE_CHECK from the device status word."""
+    s, _ = small_index()
+    ix = device_index(s)
+    sr = search.Searcher(ix, 64, 64, 32, 8)
+    tp = search.TopologySearchParams(top_l=32, search_width=2, max_expansions=512)
+    rp = search.RerankExactParams(top_k=10, top_n=32)
+    q = s.queries[:32].cpu().numpy()
+    good_ids, good_d, _ = sr.run_host(q, tp, rp, fixed_entries=np.array([s.medoid, 7], np.uint32))
+    ids = np.zeros((32, 10), np.uint32)
+    dists = np.zeros((32, 10), np.float32)
+    with pytest.raises(capi.TannError) as err:
+        sr.run_host(q, tp, rp, fixed_entries=np.array([s.medoid, ix.num_nodes + 3, 7], np.uint32), out_ids=ids, out_dists=dists)
+    assert err.value.status == 4 and "status bits 0x1" in err.value.message
+    assert np.array_equal(ids, good_ids) and np.array_equal(dists, good_d)
+    again, _, _ = sr.run_host(q, tp, rp, fixed_entries=np.array([s.medoid, 7], np.uint32))   # the word is cleared per run
+    assert np.array_equal(again, good_ids)
     sr.close()
 
 

@@ -67,3 +67,28 @@ def test_static_rerank_rejects_batches_beyond_its_area():
                                              _ptr(out_d), _ptr(out_i), None)
     assert st == 3  # TANN_ERR_UNSUPPORTED
     assert b"static area" in capi.load().tann_last_error()
+
+
+def test_static_rerank_applies_the_checks_of_the_allocating_entry_point():
+    """Rejected before any launch: early stop with a top_k beyond the kernel's 128-entry list, and a sharded
+    vector view whose rows_per_shard is zero (the kernel would divide by it)."""
+    s, _host = gs.small_index()
+    ix = gs.device_index(s)
+    q = s.queries[:4].cuda().contiguous()
+    cand = torch.zeros((4, 256, 2), dtype=torch.int32, device="cuda")
+    out_d = torch.empty((4, 200), dtype=torch.float32, device="cuda")
+    out_i = torch.empty((4, 200), dtype=torch.int32, device="cuda")
+    lib = capi.load()
+    view = ix.view()
+    p = search.RerankExactParams(top_k=200, top_n=256, use_early_stop=True).to_c()
+    st = lib.tann_rerank_topk_static(C.byref(view), C.byref(p), _ptr(cand), 256, 4, _ptr(q), 2, None, _ptr(out_d),
+                                     _ptr(out_i), None)
+    assert st == 1 and b"early stop requires 1 <= top_k <= 128" in lib.tann_last_error()
+    view = ix.view()
+    view.vectors.num_shards = 2
+    view.vectors.base[1] = view.vectors.base[0]
+    view.vectors.rows_per_shard = 0
+    p = search.RerankExactParams(top_k=10, top_n=32).to_c()
+    st = lib.tann_rerank_topk_static(C.byref(view), C.byref(p), _ptr(cand), 256, 4, _ptr(q), 2, None, _ptr(out_d),
+                                     _ptr(out_i), None)
+    assert st == 1 and b"shards do not cover all rows" in lib.tann_last_error()

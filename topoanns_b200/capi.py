@@ -142,6 +142,8 @@ SIGNATURES = {
     "tann_searcher_run_device": (_I, [_VP, C.POINTER(BeamParams), C.POINTER(RerankParams), _VP, _U32, _U64,
                                       _VP, _VP, C.POINTER(_VP), C.POINTER(_VP), C.POINTER(_VP), _VP]),
     "tann_searcher_destroy": (_I, [_VP]),
+    "tann_searcher_status_device": (_I, [_VP, C.POINTER(_VP)]),
+    "tann_dependent_load_ns": (_I, [_VP, _U64, _U32, C.POINTER(C.c_float), _VP]),
 }
 
 _lib = None

@@ -304,7 +304,6 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
     __shared__ __align__(8) unsigned long long lut_barrier;   // completion of the bulk copy of a caller's table
     uint32_t lut_phase = 0;
-    bool lut_bulk_ok = true;
     if (a.lut != nullptr) {
         if (tid == 0) BarrierInit(&lut_barrier, 1);
         __syncthreads();
@@ -327,18 +326,12 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         // ---- per-query set-up --------------------------------------------------------------
         bool lut_copy_pending = false;
         if (a.lut != nullptr) {
-            // A table given by the caller is staged with one bulk asynchronous copy (rows of 1 KB, 16-byte
-            // aligned) while the block clears its lists; a table at an odd address takes ordinary loads.
+            // A table given by the caller is staged with one bulk asynchronous copy while the block clears
+            // its lists.
             const float* src_lut = a.lut + q * (uint64_t)M * kCentroids;
-            if (lut_bulk_ok && (reinterpret_cast<uintptr_t>(src_lut) & 15u) == 0) {
-                if (tid == 0) BulkLoadToShared(lut, src_lut, M * kCentroids * 4, &lut_barrier);
-                lut_copy_pending = true;
-            } else {
-                const float4* src = reinterpret_cast<const float4*>(src_lut);
-                float4* dst = reinterpret_cast<float4*>(lut);
-#pragma unroll 8
-                for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
-            }
+            // (the host side rejects tables that are not 16-byte aligned; rows are 1 KB)
+            if (tid == 0) BulkLoadToShared(lut, src_lut, M * kCentroids * 4, &lut_barrier);
+            lut_copy_pending = true;
         } else {
             // src/search/pq_query_tables.cu:33-52
             for (uint32_t i = tid; i < d; i += kBeamThreads)
@@ -371,11 +364,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
         if (lut_copy_pending) {
             const bool arrived = BarrierWaitBounded(&lut_barrier, lut_phase & 1u);
             ++lut_phase;
-            if (!__syncthreads_and(arrived)) {   // never seen; the bounded poll keeps the block from waiting forever
-                lut_bulk_ok = false;
-                const float4* src = reinterpret_cast<const float4*>(a.lut + q * (uint64_t)M * kCentroids);
-                float4* dst = reinterpret_cast<float4*>(lut);
-                for (uint32_t i = tid; i < M * kCentroids / 4; i += kBeamThreads) dst[i] = __ldg(src + i);
+            if (!__syncthreads_and(arrived)) {
+                // Never seen. The copy may still land in `lut` later, so the block must not use that memory
+                // again: it reports the timeout, gives the copy one more bounded wait and ends without results
+                // for its remaining queries.
+                if (tid == 0 && a.status != nullptr) atomicOr(a.status, TANN_STATUS_COPY_TIMEOUT);
+                BarrierWaitBounded(&lut_barrier, (lut_phase - 1u) & 1u);
+                return;
             }
         }
         __syncthreads();
@@ -568,7 +563,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     }
                 }
                 const BloomBits bits = BloomPositions(id);
-                const bool pass = id != kInvalid && id < N && !BloomTest(bits, bloom);
+                const bool in_range = id < N;
+#ifndef TANN_BEAM_PROFILE
+                // an id that is neither the padding value nor a node of the index is skipped (as the
+                // reference does) and reported through the caller's status word
+                if (id != kInvalid && !in_range && a.status != nullptr) atomicOr(a.status, TANN_STATUS_BEAM_ID_RANGE);
+#endif
+                const bool pass = id != kInvalid && in_range && !BloomTest(bits, bloom);
                 if (kSingle) my_bits = bits;
                 // The code row does not depend on the barrier below: request it now.
                 if constexpr (kSingle && kM > 0)

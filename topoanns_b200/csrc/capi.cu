@@ -54,6 +54,8 @@ uint32_t NextPow2(uint32_t v) {
     return p;
 }
 
+}  // namespace
+namespace tann {
 TannStatus CheckShards(const TannShards& s, uint64_t rows, const char* name) {
     if (s.num_shards == 0 || s.num_shards > TANN_MAX_SHARDS)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: num_shards must be 1..%d.", name, TANN_MAX_SHARDS);
@@ -61,6 +63,17 @@ TannStatus CheckShards(const TannShards& s, uint64_t rows, const char* name) {
         if (s.base[i] == nullptr) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: shard %u has no base pointer.", name, i);
     if (s.num_shards > 1 && (s.rows_per_shard == 0 || s.rows_per_shard * s.num_shards < rows))
         return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: shards do not cover all rows.", name);
+    return TANN_OK;
+}
+}  // namespace tann
+namespace {
+using tann::CheckShards;
+
+// Rows that the kernels read with 16-byte loads must start on 16-byte boundaries.
+TannStatus CheckShardAlignment(const TannShards& s, const char* name) {
+    for (uint32_t i = 0; i < s.num_shards && i < TANN_MAX_SHARDS; ++i)
+        if ((reinterpret_cast<uintptr_t>(s.base[i]) & 15u) != 0)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: %s shard %u must be 16-byte aligned.", name, i);
     return TANN_OK;
 }
 
@@ -178,6 +191,18 @@ TannStatus tann_beam_search(const TannIndexView* index, const TannBeamParams* pa
     }
     if (!entry_offsets || !entry_ids || !out_candidates || !out_stats)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: null pointer.");
+    if (lut != nullptr && (reinterpret_cast<uintptr_t>(lut) & 15u) != 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_beam_search: the query tables must be 16-byte aligned.");
+    if (index->num_chunks % 16 == 0) {   // chunk counts with a 16-byte code row take 16-byte loads
+        st = CheckShardAlignment(index->codes, "codes");
+        if (st != TANN_OK) return st;
+        if (index->neighbor_codes.base[0] != nullptr) {
+            if (index->neighbor_codes.num_shards == 0 || index->neighbor_codes.num_shards > TANN_MAX_SHARDS)
+                return Fail(TANN_ERR_INVALID_ARGUMENT, "neighbor_codes: num_shards must be 1..%d.", TANN_MAX_SHARDS);
+            st = CheckShardAlignment(index->neighbor_codes, "neighbor_codes");
+            if (st != TANN_OK) return st;
+        }
+    }
     BeamPlan plan;
     st = PlanBeam(index, params, lut == nullptr, num_queries, &plan);
     if (st != TANN_OK) return st;
@@ -294,31 +319,38 @@ TannStatus tann_pq2_cross_terms(uint32_t dim, uint32_t num_chunks, const uint32_
 
 // Parameter rules of the rerank (src/search/rerank_exact.cu:2181-2190, :2564-2585), shared by
 // tann_rerank_exact and the searcher.
-static TannStatus CheckRerank(const TannIndexView* index, const TannRerankParams* params, const float* error_bounds) {
+}  // extern "C"
+namespace tann {
+TannStatus CheckRerank(const char* who, const TannIndexView* index, const TannRerankParams* params,
+                       const float* error_bounds) {
     if (index->vectors.base[0] == nullptr || index->vector_bytes == 0 || index->vectors_per_page == 0)
-        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: Vector store must be loaded before rerank.");
-    if (params->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "tann_rerank_exact: top_n must be at most 2048.");
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: Vector store must be loaded before rerank.", who);
+    if (params->top_n > 2048) return Fail(TANN_ERR_UNSUPPORTED, "%s: top_n must be at most 2048.", who);
     if (params->use_bound_filter) {
         if (params->top_k == 0 || params->top_k > 128)
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires 1 <= top_k <= 128.");
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: PQ2 bound filter requires 1 <= top_k <= 128.", who);
         if (error_bounds == nullptr)
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: PQ2 bound filter requires residual PQ2 error bounds.");
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: PQ2 bound filter requires residual PQ2 error bounds.", who);
     }
     if (params->use_early_stop) {
         if (params->top_k == 0 || params->top_k > 128)
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires 1 <= top_k <= 128.");
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: early stop requires 1 <= top_k <= 128.", who);
         if (params->early_stop_patience_tiles == 0)
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: early stop requires early_stop_patience_tiles >= 1.");
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: early stop requires early_stop_patience_tiles >= 1.", who);
     }
     return CheckShards(index->vectors, index->num_nodes, "vectors");
 }
+}  // namespace tann
+static TannStatus CheckRerank(const TannIndexView* index, const TannRerankParams* params, const float* error_bounds) {
+    return tann::CheckRerank("tann_rerank_exact", index, params, error_bounds);
+}
+extern "C" {
 
 TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams* params,
                              const void* candidates, uint32_t capacity, uint64_t num_queries,
                              const void* queries, uint32_t query_kind, const float* error_bounds,
                              float* out_dists, uint32_t* out_ids, unsigned long long* out_counts,
                              uint32_t* status, tann_stream_t stream) {
-    (void)status;
     if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_exact: null index or params.");
     if (num_queries == 0 || params->top_n == 0) return TANN_OK;
     if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
@@ -326,7 +358,8 @@ TannStatus tann_rerank_exact(const TannIndexView* index, const TannRerankParams*
     TannStatus st = CheckRerank(index, params, error_bounds);
     if (st != TANN_OK) return st;
     TANN_CUDA(tann::LaunchRerank(*index, *params, candidates, capacity, num_queries, queries, query_kind,
-                                 error_bounds, out_dists, out_ids, out_counts, (cudaStream_t)stream));
+                                 error_bounds, out_dists, out_ids, out_counts, (cudaStream_t)stream, nullptr, nullptr, 0,
+                                 status));
     return TANN_OK;
 }
 
@@ -457,7 +490,6 @@ TannStatus tann_rerank_exact_learned_stop(const TannIndexView* index, const Tann
                                           unsigned long long* out_counts, uint32_t* out_stop_prefixes,
                                           uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, uint32_t* status,
                                           tann_stream_t stream) {
-    (void)status;
     const char* ctx = "tann_rerank_exact_learned_stop";
     if (!index || !params) return Fail(TANN_ERR_INVALID_ARGUMENT, "%s: null index or params.", ctx);
     if (num_queries == 0 || params->top_n == 0 || capacity == 0) return TANN_OK;
@@ -490,7 +522,7 @@ TannStatus tann_rerank_exact_learned_stop(const TannIndexView* index, const Tann
     TANN_CUDA(tann::LaunchRerankLearned(*index, *params, m, use_schedule, use_schedule && replay_stop_prefixes == nullptr,
                                         candidates, capacity, num_queries, queries, query_kind, error_bounds,
                                         replay_stop_prefixes, out_dists, out_ids, out_counts, out_stop_prefixes,
-                                        out_checkpoint_counts, out_stop_flags, (cudaStream_t)stream));
+                                        out_checkpoint_counts, out_stop_flags, (cudaStream_t)stream, status));
     return TANN_OK;
 }
 
@@ -579,6 +611,40 @@ TannStatus tann_enable_peer_access(int peer_device) {
     return TANN_OK;
 }
 
+// ---- measurement aid: one dependent random load after another ----------------------------------------
+__global__ void dependent_load_kernel(const uint32_t* base, uint64_t words, uint32_t steps, float* out_ns) {
+    uint64_t pos = 0x9e3779b97f4a7c15ull % words;
+    uint32_t acc = 0;
+    unsigned long long t0, t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t i = 0; i < steps; ++i) {
+        const uint32_t v = __ldcg(base + pos);   // the next address depends on the value just read
+        acc += v;
+        pos = ((pos + v) * 6364136223846793005ull + 1442695040888963407ull + i) % words;
+    }
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    out_ns[0] = steps ? (float)((double)(t1 - t0) / (double)steps) : 0.0f;
+    out_ns[1] = __uint_as_float(acc);   // keeps the loads alive
+}
+
+TannStatus tann_dependent_load_ns(const void* base, uint64_t bytes, uint32_t steps, float* out_ns, tann_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!base || !out_ns || bytes < 4 || steps == 0)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_dependent_load_ns: null pointer or empty range.");
+    if (steps > (1u << 20)) return Fail(TANN_ERR_UNSUPPORTED, "tann_dependent_load_ns: at most 2^20 steps.");
+    float* d_out = nullptr;
+    TANN_CUDA(cudaMalloc((void**)&d_out, 2 * sizeof(float)));
+    dependent_load_kernel<<<1, 1, 0, stream>>>(static_cast<const uint32_t*>(base), bytes / 4, steps, d_out);
+    cudaError_t e = cudaGetLastError();
+    float host[2] = {0.0f, 0.0f};
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host, d_out, sizeof(host), cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    cudaFree(d_out);
+    if (e != cudaSuccess) return CudaFail(e, "tann_dependent_load_ns");
+    *out_ns = host[0];
+    return TANN_OK;
+}
+
 // ---- searcher -----------------------------------------------------------------------------------
 
 struct TannSearcher {
@@ -606,6 +672,9 @@ struct TannSearcher {
     float* d_topk_dists;
     uint32_t* d_topk_ids;
     unsigned long long* d_counts;
+    uint32_t* d_fixed_entries;   // max_entries ids: the fixed entry list before it is expanded per query
+    uint32_t* d_status;          // TANN_STATUS_* bits of the last run
+    uint32_t* h_status;
     // pinned staging
     // a batch that tann_searcher_submit enqueued and tann_searcher_wait has not collected yet
     struct Pending {
@@ -628,7 +697,8 @@ static void FreeSearcher(TannSearcher* s) {
     cudaFree(s->d_queries); cudaFree(s->d_queries_f32); cudaFree(s->d_queries_u8); cudaFree(s->d_not_u8); cudaFree(s->d_entry_offsets);
     cudaFree(s->d_entry_ids); cudaFree(s->d_cand); cudaFree(s->d_cand_refined); cudaFree(s->d_stats);
     cudaFree(s->d_lut2); cudaFree(s->d_dists); cudaFree(s->d_ids); cudaFree(s->d_topk_dists);
-    cudaFree(s->d_topk_ids); cudaFree(s->d_counts);
+    cudaFree(s->d_topk_ids); cudaFree(s->d_counts); cudaFree(s->d_fixed_entries); cudaFree(s->d_status);
+    cudaFreeHost(s->h_status);
     cudaFreeHost(s->h_queries); cudaFreeHost(s->h_topk_ids); cudaFreeHost(s->h_topk_dists);
     cudaFreeHost(s->h_stats); cudaFreeHost(s->h_entries);
     cudaGetLastError();
@@ -670,6 +740,9 @@ TannStatus tann_searcher_create(const TannIndexView* index, uint64_t max_queries
     dev((void**)&s->d_topk_dists, Q * max_top_n * 4);
     dev((void**)&s->d_topk_ids, Q * max_top_n * 4);
     dev((void**)&s->d_counts, 16);
+    dev((void**)&s->d_fixed_entries, (size_t)max_entries_per_query * 4);
+    dev((void**)&s->d_status, 16);
+    host((void**)&s->h_status, 16);
     host(&s->h_queries, Q * d * 4);
     host((void**)&s->h_topk_ids, Q * max_top_n * 4);
     host((void**)&s->h_topk_dists, Q * max_top_n * 4);
@@ -737,6 +810,7 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
     if (rerank->top_n > beam->candidate_capacity)
         return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: top_n exceeds the candidate capacity.");
     if (Q == 0) return TANN_OK;
+    TANN_CUDA(cudaMemsetAsync(s->d_status, 0, sizeof(uint32_t), stream));
     const uint32_t d = s->ix.dim;
     const float* qf32 = static_cast<const float*>(queries_dev);
     const bool need_f32 = (s->has_rvq && entry_offsets_dev == nullptr) || s->has_pq2;
@@ -751,17 +825,19 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
     if (eo == nullptr) {
         if (!s->has_rvq) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: no entries and no RVQ model.");
         const TannRvqModelView& r = s->rvq;
-        TannStatus st = tann_rvq_entries(qf32, Q, d, r.coarse, r.coarse_t, r.coarse_norms, r.num_coarse,
-                                         r.fine_t, r.fine_norms, r.num_fine, r.bucket_sizes,
-                                         r.cluster_offsets, r.cluster_ids, r.entry_count, r.fallback_entry,
-                                         nullptr, s->d_entry_ids, s->d_entry_offsets, stream);
-        if (st != TANN_OK) return st;
+        if (!r.coarse || !r.coarse_t || !r.coarse_norms || !r.fine_t || !r.fine_norms || !r.bucket_sizes ||
+            !r.cluster_offsets || !r.cluster_ids || r.num_coarse == 0 || r.num_fine == 0)
+            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_rvq_entries: model is not loaded.");
+        TANN_CUDA(tann::LaunchRvqEntries(qf32, Q, d, r.coarse, r.coarse_t, r.coarse_norms, r.num_coarse, r.fine_t,
+                                         r.fine_norms, r.num_fine, r.bucket_sizes, r.cluster_offsets, r.cluster_ids,
+                                         r.entry_count, r.fallback_entry, nullptr, s->d_entry_ids, s->d_entry_offsets,
+                                         stream, s->d_status));
         eo = s->d_entry_offsets;
         ei = s->d_entry_ids;
     }
     // traversal, table built in the kernel
     TannStatus st = tann_beam_search(&s->ix, beam, nullptr, queries_dev, query_kind, Q, eo, ei, s->d_cand,
-                                     s->d_stats, nullptr, stream);
+                                     s->d_stats, s->d_status, stream);
     if (st != TANN_OK) return st;
     const void* cand = s->d_cand;
     uint32_t capacity = beam->candidate_capacity;
@@ -787,7 +863,7 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         // persistent rerank with the learned stop: keeps the top_k list itself, nothing to pack
         st = tann_rerank_exact_learned_stop(&s->ix, rerank, &s->rerank_stop, cand, capacity, Q, queries_dev, query_kind, err,
                                             nullptr, s->d_topk_dists, s->d_topk_ids, nullptr, nullptr, nullptr, nullptr,
-                                            nullptr, stream);
+                                            s->d_status, stream);
         if (st != TANN_OK) return st;
         if (out_ids_dev) *out_ids_dev = s->d_topk_ids;
         if (out_dists_dev) *out_dists_dev = s->d_topk_dists;
@@ -804,7 +880,8 @@ TannStatus tann_searcher_run_device(TannSearcher* s, const TannBeamParams* beam,
         // only the first top_k ranks are packed below: a top-k tournament replaces the full sort when k <= 32
         TANN_CUDA(tann::LaunchRerank(s->ix, *rerank, cand, capacity, Q, queries_dev, query_kind, err, s->d_dists,
                                      s->d_ids, nullptr, stream, u8_copy ? s->d_queries_u8 : nullptr,
-                                     u8_copy ? s->d_not_u8 : nullptr, rerank->top_k <= 32 ? rerank->top_k : 0));
+                                     u8_copy ? s->d_not_u8 : nullptr, rerank->top_k <= 32 ? rerank->top_k : 0,
+                                     s->d_status));
     }
     st = tann_topk_pack(s->d_dists, s->d_ids, Q, rerank->top_n, rerank->top_k, s->d_topk_dists,
                         s->d_topk_ids, stream);
@@ -835,32 +912,45 @@ TannStatus tann_searcher_submit(TannSearcher* s, const TannBeamParams* beam, con
         memcpy(s->h_queries, queries_host, qbytes);
         h2d_src = s->h_queries;
     }
-    TANN_CUDA(cudaMemcpyAsync(s->d_queries, h2d_src, qbytes, cudaMemcpyHostToDevice, stream));
+    if (fixed_entries_host != nullptr && num_fixed_entries > s->max_entries)
+        return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: too many fixed entries.");
+    // From here on work is enqueued on the stream: an error return first lets it drain, so that the caller's
+    // buffers are no longer in use when the call comes back.
+    const auto drained = [&](TannStatus st) {
+        cudaStreamSynchronize(stream);
+        return st;
+    };
+    cudaError_t ce = cudaMemcpyAsync(s->d_queries, h2d_src, qbytes, cudaMemcpyHostToDevice, stream);
+    if (ce != cudaSuccess) return drained(CudaFail(ce, "cudaMemcpyAsync(queries)"));
     const uint32_t* eo = nullptr;
     const uint32_t* ei = nullptr;
     if (fixed_entries_host != nullptr && num_fixed_entries != 0) {
-        if (num_fixed_entries > s->max_entries)
-            return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_run: too many fixed entries.");
         memcpy(s->h_entries, fixed_entries_host, (size_t)num_fixed_entries * 4);
-        // stage the list behind the per-query id array, then expand it on the device
-        uint32_t* d_list = reinterpret_cast<uint32_t*>(s->d_topk_ids);  // free until the last step
-        TANN_CUDA(cudaMemcpyAsync(d_list, s->h_entries, (size_t)num_fixed_entries * 4, cudaMemcpyHostToDevice, stream));
-        fixed_entries_kernel<<<tann::SmCount() * 2, 256, 0, stream>>>(d_list, num_fixed_entries, Q,
+        // the list goes to its own max_entries-sized buffer, then is expanded per query on the device
+        ce = cudaMemcpyAsync(s->d_fixed_entries, s->h_entries, (size_t)num_fixed_entries * 4, cudaMemcpyHostToDevice, stream);
+        if (ce != cudaSuccess) return drained(CudaFail(ce, "cudaMemcpyAsync(fixed entries)"));
+        fixed_entries_kernel<<<tann::SmCount() * 2, 256, 0, stream>>>(s->d_fixed_entries, num_fixed_entries, Q,
                                                                       s->d_entry_offsets, s->d_entry_ids);
-        TANN_CUDA(cudaGetLastError());
+        ce = cudaGetLastError();
+        if (ce != cudaSuccess) return drained(CudaFail(ce, "fixed_entries_kernel"));
         eo = s->d_entry_offsets;
         ei = s->d_entry_ids;
     }
     TannStatus st = tann_searcher_run_device(s, beam, rerank, s->d_queries, query_kind, Q, eo, ei, nullptr,
                                              nullptr, nullptr, stream);
-    if (st != TANN_OK) return st;
+    if (st != TANN_OK) return drained(st);
     const size_t kbytes = Q * (size_t)rerank->top_k * 4;
     const bool ids_direct = IsPageLocked(out_ids_host), dists_direct = IsPageLocked(out_dists_host);
-    TANN_CUDA(cudaMemcpyAsync(ids_direct ? (void*)out_ids_host : (void*)s->h_topk_ids, s->d_topk_ids, kbytes,
-                              cudaMemcpyDeviceToHost, stream));
-    TANN_CUDA(cudaMemcpyAsync(dists_direct ? (void*)out_dists_host : (void*)s->h_topk_dists, s->d_topk_dists, kbytes,
-                              cudaMemcpyDeviceToHost, stream));
-    if (out_stats_host) TANN_CUDA(cudaMemcpyAsync(s->h_stats, s->d_stats, Q * 32, cudaMemcpyDeviceToHost, stream));
+    ce = cudaMemcpyAsync(ids_direct ? (void*)out_ids_host : (void*)s->h_topk_ids, s->d_topk_ids, kbytes,
+                         cudaMemcpyDeviceToHost, stream);
+    if (ce == cudaSuccess)
+        ce = cudaMemcpyAsync(dists_direct ? (void*)out_dists_host : (void*)s->h_topk_dists, s->d_topk_dists, kbytes,
+                             cudaMemcpyDeviceToHost, stream);
+    if (ce == cudaSuccess && out_stats_host)
+        ce = cudaMemcpyAsync(s->h_stats, s->d_stats, Q * 32, cudaMemcpyDeviceToHost, stream);
+    if (ce == cudaSuccess)
+        ce = cudaMemcpyAsync(s->h_status, s->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream);
+    if (ce != cudaSuccess) return drained(CudaFail(ce, "cudaMemcpyAsync(results)"));
     s->pending.active = true;
     s->pending.stream = stream;
     s->pending.out_ids = ids_direct ? nullptr : out_ids_host;
@@ -879,6 +969,11 @@ TannStatus tann_searcher_wait(TannSearcher* s) {
     if (s->pending.out_ids) memcpy(s->pending.out_ids, s->h_topk_ids, s->pending.kbytes);
     if (s->pending.out_dists) memcpy(s->pending.out_dists, s->h_topk_dists, s->pending.kbytes);
     if (s->pending.out_stats) memcpy(s->pending.out_stats, s->h_stats, s->pending.stats_bytes);
+    if (*s->h_status != 0u)
+        return Fail(TANN_ERR_DEVICE_CHECK,
+                    "tann_searcher_run: a kernel skipped an index outside the index view (status bits 0x%x: 1 = entry or "
+                    "adjacency id, 2 = rerank candidate id, 4 = shared-memory copy timeout); results cover the rest.",
+                    *s->h_status);
     return TANN_OK;
 }
 
@@ -894,6 +989,12 @@ TannStatus tann_searcher_run(TannSearcher* s, const TannBeamParams* beam, const 
         return st;
     }
     return tann_searcher_wait(s);
+}
+
+TannStatus tann_searcher_status_device(TannSearcher* s, const uint32_t** out_status_dev) {
+    if (!s || !out_status_dev) return Fail(TANN_ERR_INVALID_ARGUMENT, "tann_searcher_status_device: null pointer.");
+    *out_status_dev = s->d_status;
+    return TANN_OK;
 }
 
 TannStatus tann_searcher_destroy(TannSearcher* s) {

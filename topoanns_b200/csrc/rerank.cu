@@ -286,7 +286,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
               const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
               uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts,
               const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag,
-              uint32_t final_ranks) {
+              uint32_t final_ranks, uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char rr_smem[];
     // keys[r] first holds the address of candidate r's vector (or the invalid key when the rank is
     // empty or filtered), then its (distance, id) sort key.
@@ -353,6 +353,8 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
                 if (r < capacity) {
                     const Cand c = cand[q * capacity + r];
                     const uint32_t id = c.id & kRawMask;
+                    if (c.id != kInvalid && id >= ix.num_nodes && status != nullptr)
+                        atomicOr(status, TANN_STATUS_RERANK_ID_RANGE);   // skipped, and reported
                     if (c.id != kInvalid && id < ix.num_nodes) {
                         bool keep = true;
                         if (p.use_bound_filter && isfinite(threshold))
@@ -522,7 +524,8 @@ rerank_learned_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams
                       uint32_t qkind, const float* __restrict__ error_bounds, const uint32_t* __restrict__ replay,
                       uint32_t padded, float* __restrict__ out_dists, uint32_t* __restrict__ out_ids,
                       unsigned long long* __restrict__ out_counts, uint32_t* __restrict__ out_stop_prefixes,
-                      uint32_t* __restrict__ out_checkpoints, uint32_t* __restrict__ out_stop_flags) {
+                      uint32_t* __restrict__ out_checkpoints, uint32_t* __restrict__ out_stop_flags,
+                      uint32_t* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char rr_smem[];
     unsigned long long* keys = reinterpret_cast<unsigned long long*>(rr_smem);   // [padded]
     uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
@@ -583,6 +586,8 @@ rerank_learned_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams
                 unsigned long long slot = kInvalidKey64;
                 const Cand c = cand[q * capacity + r];
                 const uint32_t id = c.id & kRawMask;
+                if (c.id != kInvalid && id >= ix.num_nodes && status != nullptr)
+                    atomicOr(status, TANN_STATUS_RERANK_ID_RANGE);   // skipped, and reported
                 if (c.id != kInvalid && id < ix.num_nodes) {
                     bool keep = true;
                     if (p.use_bound_filter && isfinite(threshold))
@@ -737,7 +742,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
                          uint32_t capacity, uint64_t Q, const void* queries, uint32_t query_kind,
                          const float* error_bounds, float* out_dists, uint32_t* out_ids,
                          unsigned long long* out_counts, cudaStream_t stream, const uint8_t* queries_u8,
-                         const uint32_t* not_u8_flag, uint32_t final_ranks) {
+                         const uint32_t* not_u8_flag, uint32_t final_ranks, uint32_t* status) {
     if (Q == 0 || p.top_n == 0) return cudaSuccess;
     uint32_t padded = 1;
     while (padded < p.top_n) padded <<= 1;
@@ -751,7 +756,7 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     const uint64_t cap = (uint64_t)SmCount() * 8;
     rerank_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, static_cast<const Cand*>(cand), capacity, Q, queries, query_kind, error_bounds, padded,
-        out_dists, out_ids, out_counts, queries_u8, not_u8_flag, final_ranks);
+        out_dists, out_ids, out_counts, queries_u8, not_u8_flag, final_ranks, status);
     return cudaGetLastError();
 }
 
@@ -760,7 +765,8 @@ cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams&
                                 const void* queries, uint32_t query_kind, const float* error_bounds,
                                 const uint32_t* replay_stop_prefixes, float* out_dists, uint32_t* out_ids,
                                 unsigned long long* out_counts, uint32_t* out_stop_prefixes,
-                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream) {
+                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream,
+                                uint32_t* status) {
     if (Q == 0 || p.top_n == 0 || capacity == 0) return cudaSuccess;
     const uint32_t budget = p.top_n < capacity ? p.top_n : capacity;
     uint32_t padded = 1;
@@ -776,7 +782,7 @@ cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams&
     rerank_learned_kernel<<<(unsigned)(Q < cap ? Q : cap), kRerankThreads, smem, stream>>>(
         ix, p, model, use_schedule ? 1u : 0u, evaluate ? 1u : 0u, static_cast<const Cand*>(cand), capacity, Q, queries,
         query_kind, error_bounds, replay_stop_prefixes, padded, out_dists, out_ids, out_counts, out_stop_prefixes,
-        out_checkpoint_counts, out_stop_flags);
+        out_checkpoint_counts, out_stop_flags, status);
     return cudaGetLastError();
 }
 

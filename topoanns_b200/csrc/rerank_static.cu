@@ -76,18 +76,17 @@ extern "C" TannStatus tann_rerank_topk_static(const TannIndexView* index, const 
     if (num_queries == 0 || params->top_k == 0) return TANN_OK;
     if (!candidates || !queries || !out_dists || !out_ids || query_kind > TANN_KIND_FLOAT32)
         return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: null pointer or unknown query kind.");
-    if (index->vectors.base[0] == nullptr || index->vector_bytes == 0 || index->vectors_per_page == 0)
-        return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: Vector store must be loaded before rerank.");
-    if (index->vectors.num_shards == 0 || index->vectors.num_shards > TANN_MAX_SHARDS)
-        return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: vectors: bad shard count.");
-    if (params->top_n == 0 || params->top_n > 2048)
-        return StaticFail(TANN_ERR_UNSUPPORTED, "tann_rerank_topk_static: top_n must be 1..2048.");
-    if (params->use_bound_filter) {
-        if (params->top_k > 128)
-            return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: PQ2 bound filter requires 1 <= top_k <= 128.");
-        if (error_bounds == nullptr)
-            return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: PQ2 bound filter requires residual PQ2 error bounds.");
-    }
+    if (params->top_n == 0) return StaticFail(TANN_ERR_UNSUPPORTED, "tann_rerank_topk_static: top_n must be 1..2048.");
+    // the rules of tann_rerank_exact (vector store, top_n, bound filter, early stop, shard coverage)
+    TannStatus st = tann::CheckRerank("tann_rerank_topk_static", index, params, error_bounds);
+    if (st != TANN_OK) return st;
+    if (params->top_k > params->top_n)
+        return StaticFail(TANN_ERR_INVALID_ARGUMENT, "tann_rerank_topk_static: need top_k <= top_n.");
+    // bounds the products below well inside size_t before they are formed
+    if (num_queries > (uint64_t)TANN_STATIC_SCRATCH_BYTES || index->dim > (uint32_t)TANN_STATIC_SCRATCH_BYTES)
+        return StaticFail(TANN_ERR_UNSUPPORTED,
+                          "tann_rerank_topk_static: batch is larger than the static work space; split the batch or use "
+                          "tann_rerank_exact.");
     const bool u8_copy = query_kind == TANN_KIND_FLOAT32 && index->vector_kind == TANN_KIND_UINT8 &&
                          !params->use_bound_filter;
     const size_t flag_bytes = 256;
@@ -102,7 +101,7 @@ extern "C" TannStatus tann_rerank_topk_static(const TannIndexView* index, const 
         return StaticFail(TANN_ERR_UNSUPPORTED, msg);
     }
     unsigned char* scratch = nullptr;
-    TannStatus st = ScratchForCurrentDevice(&scratch);
+    st = ScratchForCurrentDevice(&scratch);
     if (st != TANN_OK) return st;
     uint32_t* flag = reinterpret_cast<uint32_t*>(scratch);
     uint8_t* q8 = scratch + flag_bytes;

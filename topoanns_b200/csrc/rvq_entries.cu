@@ -367,7 +367,7 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
                         const int32_t* __restrict__ bucket_sizes, const uint32_t* __restrict__ cluster_offsets,
                         const uint32_t* __restrict__ cluster_ids, uint32_t entry_count, uint32_t fallback,
                         int32_t* __restrict__ out_clusters, uint32_t* __restrict__ out_entry_ids,
-                        uint32_t* __restrict__ out_entry_offsets, uint32_t per_block) {
+                        uint32_t* __restrict__ out_entry_offsets, uint32_t per_block, uint32_t* __restrict__ status) {
     constexpr int QB = kSmemTile;
     constexpr int XS = kSmemTile + 4;   // row stride of x: keeps 16-byte alignment, spreads a column over 8 banks
     constexpr int kWarps = kSmemThreads / 32;
@@ -389,7 +389,7 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
     if (q_begin >= Q) return;
     const uint32_t n_mine = (uint32_t)min((uint64_t)per_block, Q - q_begin);
     if (tid == 0) BarrierInit(&copy_barrier, 1);
-    bool bulk_ok = true;   // block-uniform: cleared if a bulk copy did not complete in time
+    const bool bulk_ok = true;   // the level's codebook arrives by one bulk copy
 
     for (int level = 0; level < 2; ++level) {
         const float* book_t = level == 0 ? coarse_t : fine_t;
@@ -443,12 +443,13 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
             __syncthreads();
             if (bulk && t0 == 0) {
                 const bool arrived = BarrierWaitBounded(&copy_barrier, (uint32_t)level & 1u);
-                if (!__syncthreads_and(arrived)) {   // never seen; the bounded poll keeps the block from waiting forever
-                    bulk_ok = false;
-#pragma unroll 8
-                    for (uint32_t i = tid; i < book_bytes / 16; i += kSmemThreads)
-                        reinterpret_cast<float4*>(cb)[i] = __ldg(reinterpret_cast<const float4*>(book_t) + i);
-                    __syncthreads();
+                if (!__syncthreads_and(arrived)) {
+                    // Never seen. The copy may still land in `cb` later, so the block must not use that memory
+                    // again: it reports the timeout, gives the copy one more bounded wait and ends without
+                    // entries for its queries.
+                    if (tid == 0 && status != nullptr) atomicOr(status, TANN_STATUS_COPY_TIMEOUT);
+                    BarrierWaitBounded(&copy_barrier, (uint32_t)level & 1u);
+                    return;
                 }
             }
             ArgMin best[8];
@@ -559,7 +560,7 @@ cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, con
                              const int32_t* bucket_sizes, const uint32_t* cluster_offsets,
                              const uint32_t* cluster_ids, uint32_t entry_count, uint32_t fallback,
                              int32_t* out_clusters, uint32_t* out_entry_ids,
-                             uint32_t* out_entry_offsets, cudaStream_t stream) {
+                             uint32_t* out_entry_offsets, cudaStream_t stream, uint32_t* status) {
     if (Q == 0) return cudaSuccess;
     // codebooks that fit shared memory next to a 64-query tile: one resident block per SM
     {
@@ -580,7 +581,7 @@ cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, con
             rvq_entries_smem_kernel<<<(unsigned)blocks, kSmemThreads, smem, stream>>>(
                 queries, Q, dim, coarse, coarse_t, coarse_norms, nc, fine_t, fine_norms, nf, bucket_sizes,
                 cluster_offsets, cluster_ids, entry_count, fallback, out_clusters, out_entry_ids,
-                out_entry_offsets, (uint32_t)per);
+                out_entry_offsets, (uint32_t)per, status);
             return cudaGetLastError();
         }
     }

@@ -29,7 +29,8 @@ cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, con
                              const int32_t* bucket_sizes, const uint32_t* cluster_offsets,
                              const uint32_t* cluster_ids, uint32_t entry_count, uint32_t fallback,
                              int32_t* out_clusters, uint32_t* out_entry_ids,
-                             uint32_t* out_entry_offsets, cudaStream_t stream);
+                             uint32_t* out_entry_offsets, cudaStream_t stream,
+                             uint32_t* status = nullptr /* dev: TANN_STATUS_* bits are or-ed in */);
 
 cudaError_t LaunchPq2Refine(const void* cand, const uint32_t* stats, uint64_t Q, uint32_t capacity,
                             uint32_t refine_top_l, const TannShards* base_codes,
@@ -52,14 +53,16 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
                          unsigned long long* out_counts, cudaStream_t stream,
                          const uint8_t* queries_u8 = nullptr, const uint32_t* not_u8_flag = nullptr,
                          uint32_t final_ranks = 0 /* > 0: only the first final_ranks (<= 32) entries of every
-                                                     output list are produced (the smallest, in order) */);
+                                                     output list are produced (the smallest, in order) */,
+                         uint32_t* status = nullptr /* dev: TANN_STATUS_* bits are or-ed in */);
 // Rerank with the learned stop / stage schedule / stop-prefix replay; out lists are [Q][top_k].
 cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams& p, const TannRerankLearnedStop& model,
                                 bool use_schedule, bool evaluate, const void* cand, uint32_t capacity, uint64_t Q,
                                 const void* queries, uint32_t query_kind, const float* error_bounds,
                                 const uint32_t* replay_stop_prefixes, float* out_dists, uint32_t* out_ids,
                                 unsigned long long* out_counts, uint32_t* out_stop_prefixes,
-                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream);
+                                uint32_t* out_checkpoint_counts, uint32_t* out_stop_flags, cudaStream_t stream,
+                                uint32_t* status = nullptr);
 cudaError_t LaunchF32ToU8Checked(const float* src, uint64_t n, uint8_t* dst, uint32_t* not_u8_flag,
                                  cudaStream_t stream);
 cudaError_t LaunchTopkPack(const float* dists, const uint32_t* ids, uint64_t Q, uint32_t top_n,
@@ -69,5 +72,10 @@ cudaError_t LaunchNeighborCodes(const TannIndexView& ix, uint64_t first_node, ui
                                 cudaStream_t stream);
 
 int SmCount();
+
+// Argument checks shared by the rerank entry points (messages start with `who`); they set tann_last_error.
+TannStatus CheckShards(const TannShards& s, uint64_t rows, const char* name);
+TannStatus CheckRerank(const char* who, const TannIndexView* index, const TannRerankParams* params,
+                       const float* error_bounds);
 
 }  // namespace tann

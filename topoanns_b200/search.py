@@ -172,8 +172,10 @@ def lut_build(index: DeviceIndex, queries: torch.Tensor, *, tables_col_major=Non
 
 def beam_search(index: DeviceIndex, params: TopologySearchParams, entry_offsets: torch.Tensor,
                 entry_ids: torch.Tensor, *, lut: Optional[torch.Tensor] = None,
-                queries: Optional[torch.Tensor] = None, capacity: Optional[int] = None):
-    """Returns (candidates [Q, C, 2] int32 {dist bits, packed id}, stats [Q, 8] int32)."""
+                queries: Optional[torch.Tensor] = None, capacity: Optional[int] = None,
+                status: Optional[torch.Tensor] = None):
+    """Returns (candidates [Q, C, 2] int32 {dist bits, packed id}, stats [Q, 8] int32). `status`: an int32 device
+    tensor of one element the kernel ors its TANN_STATUS_* bits into (ids outside the index are skipped)."""
     Q = entry_offsets.numel() - 1
     cap = capacity or params.capacity()
     dev = entry_offsets.device
@@ -184,7 +186,7 @@ def beam_search(index: DeviceIndex, params: TopologySearchParams, entry_offsets:
     capi.check(capi.load().tann_beam_search(
         C.byref(view), C.byref(p), _ptr(lut), _ptr(queries),
         kind_of(queries) if queries is not None else capi.KIND_FLOAT32, Q, _ptr(entry_offsets),
-        _ptr(entry_ids), _ptr(cand), _ptr(stats), None, _stream_ptr()))
+        _ptr(entry_ids), _ptr(cand), _ptr(stats), _ptr(status), _stream_ptr()))
     return cand, stats
 
 

@@ -268,6 +268,7 @@ def build(cfg: SynthConfig, device="cpu") -> SynthIndex:
     idx = SynthIndex(cfg, vectors, adjacency, tables, centroid, offs, codes, queries, gt_ids, medoid)
     idx.extras["component_of"] = component_of
     idx.extras["query_component"] = qcomp
+    idx.extras["centres"], idx.extras["basis"] = centres, basis
     if cfg.pq2:
         recon = torch.empty((N, d), dtype=torch.float32, device=dev) if N <= (1 << 24) else None
         res_sample = xs - decode_pq(codes[sample], tables, centroid, offs)
@@ -304,6 +305,14 @@ def build(cfg: SynthConfig, device="cpu") -> SynthIndex:
         idx.rvq_coarse, idx.rvq_fine = coarse, fine
         idx.rvq_buckets = [sizes.to(torch.int32), offsets.to(torch.int32), order[keep].to(torch.int32)]
     return idx
+
+
+def more_queries(cfg: SynthConfig, centres: torch.Tensor, count: int, seed: int, basis=None) -> torch.Tensor:
+    """`count` further queries from the mixture an index was drawn from (its centres are kept in
+    SynthIndex.extras["centres"]), from their own seeded stream; float32 [count, dim]."""
+    gen = _gen(centres.device, seed)
+    qcomp = torch.randint(0, centres.shape[0], (count,), generator=gen, device=centres.device)
+    return _sample_component(cfg, centres, qcomp, gen, basis).float()
 
 
 def recall_at_k(result_ids: np.ndarray, gt_ids: np.ndarray, k: int) -> float:

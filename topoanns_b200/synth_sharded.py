@@ -37,6 +37,7 @@ class ShardedSynth:
     rvq_coarse: Optional[torch.Tensor] = None
     rvq_fine: Optional[torch.Tensor] = None
     rvq_buckets: Optional[list] = None   # (sizes, offsets, ids) over the whole index, identical on every rank
+    centres: Optional[torch.Tensor] = None   # mixture centres (identical on every rank), for drawing further queries
 
 
 def _coprime_multiplier(n: int) -> int:
@@ -174,6 +175,7 @@ def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
     order = torch.argsort(cat_d, dim=1, stable=True)[:, :cfg.top_k]
     gt = cat_i.gather(1, order)
     out = ShardedSynth(cfg, world, rank, n_tot, n_loc, vectors, adjacency, codes, tables, centroid, offs, queries, gt)
+    out.centres = centres
     if cfg.rvq:
         nc, nf = coarse.shape[0], fine.shape[0]
         cluster = torch.empty(n_loc, dtype=torch.int64, device=dev)
