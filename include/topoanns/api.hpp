@@ -277,6 +277,32 @@ private:
     std::uint8_t* mapped_device_codes_ = nullptr;
 };
 
+// ---- hybrid PQ index (reference: hpq_index.hpp) -------------------------------------------------------
+// One hybrid code per chunk plus one selector bit per chunk that picks the base or the outlier codebook
+// (include/topoanns/hpq_index.hpp:13-44, src/io/hpq_index.cpp). Codes and selector bits stay in pinned,
+// device-mapped host memory as in the reference; tann_hpq_refine reads them from there or from HBM.
+class HpqIndex {
+public:
+    HpqIndex() = default;
+    ~HpqIndex();
+    HpqIndex(HpqIndex&& other) noexcept;
+    HpqIndex& operator=(HpqIndex&& other) noexcept;
+    HpqIndex(const HpqIndex&) = delete;
+    HpqIndex& operator=(const HpqIndex&) = delete;
+    static HpqIndex Load(const std::filesystem::path& base_pivots_path, const std::filesystem::path& outlier_pivots_path,
+                         const std::filesystem::path& hybrid_codes_path, const std::filesystem::path& selector_bits_path);
+    const PqIndex& base_index() const { return base_index_; }
+    const PqIndex& outlier_index() const { return outlier_index_; }
+    std::size_t selector_stride_bytes() const { return selector_stride_bytes_; }
+    const std::uint8_t* device_selector_bits() const { return mapped_device_selector_bits_; }
+private:
+    void Release() noexcept;
+    PqIndex base_index_, outlier_index_;
+    std::size_t selector_stride_bytes_ = 0;
+    std::uint8_t* mapped_host_selector_bits_ = nullptr;
+    std::uint8_t* mapped_device_selector_bits_ = nullptr;
+};
+
 // ---- query tables and the distance oracle (reference: pq_query_tables.hpp, pq_distance_oracle.hpp) --
 struct PqQueryTablesProfile {
     double total_ms = 0.0, query_upload_ms = 0.0, zero_fill_ms = 0.0, kernel_ms = 0.0, table_download_ms = 0.0;
@@ -485,6 +511,12 @@ public:
     const CudaBuffer<float>& pq2_cross_terms() const;
     const CudaBuffer<float>& pq2_error_bounds_fp32() const;
 
+    // include/topoanns/search_resources.hpp:52-57
+    void LoadHpqIndex(const std::filesystem::path& base_pivots_path, const std::filesystem::path& outlier_pivots_path,
+                      const std::filesystem::path& hybrid_codes_path, const std::filesystem::path& selector_bits_path);
+    bool has_hpq_index() const { return static_cast<bool>(hpq_index_); }
+    const HpqIndex& hpq_index() const;
+
     void LoadVectorStore(const std::filesystem::path& path);
     bool has_vector_store() const { return static_cast<bool>(vector_store_); }
     const VectorStoreHeader& vector_store_header() const;
@@ -529,6 +561,7 @@ private:
     std::shared_ptr<PinnedTopology> topology_ = std::make_shared<PinnedTopology>();
     std::shared_ptr<VectorPageProvider> topology_page_provider_;
     std::shared_ptr<PqIndex> pq_index_, pq2_index_;
+    std::shared_ptr<HpqIndex> hpq_index_;
     std::shared_ptr<Pq2Aux> pq2_aux_;
     std::shared_ptr<VectorStore> vector_store_;
     bool has_adjacency_shards_ = false, has_code_shards_ = false;
@@ -600,6 +633,20 @@ public:
                                                       const PqDistanceOracle& distance_oracle,
                                                       const TopologySearchParams& params,
                                                       TopologySearchBatchProfile* out_profile = nullptr);
+};
+
+// Hybrid-PQ refine of a traversal's candidate lists (the reference keeps this step in its private header
+// src/search/fused_rerank_device.hpp:63 as detail::RunHpqRefineBatchDevice and reaches it from its overlap
+// pipeline tool only): the traversal runs on the device, the first refine_top_l candidates of every query are
+// re-scored with the hybrid codes of resources.hpq_index() and re-sorted by (distance, id).
+class HpqRefine {
+public:
+    static std::vector<std::vector<RankedCandidate>> RunBatchFloat32(const SearchResources& resources,
+                                                                    const DeviceEntryBatch& entry_batch,
+                                                                    const std::vector<float>& queries,
+                                                                    std::size_t num_queries,
+                                                                    const TopologySearchParams& topology_params,
+                                                                    std::size_t refine_top_l);
 };
 
 // ---- rerank (reference: rerank_exact.hpp) -----------------------------------------------------------------

@@ -5,8 +5,16 @@
 //   ref_driver <dir> <out_prefix> <mode> top_l search_width max_expansions top_k top_n [rerank_mode tile pq2 bound repeats]
 //     dir: topology.bin, _pq_pivots.bin, _pq_compressed.bin, vectors.ssd, queries.fbin, entries.bin
 //          (+ _pq2_pivots.bin, _pq2_compressed.bin, _pq2_error.bin when pq2 = 1)
-//     mode: lut | search | e2e_f32 | e2e_u8 | fused
+//     mode: lut | search | e2e_f32 | e2e_u8 | fused | pq2refine | rvq | hpq | time
+//       rvq:  dir/rvq_model.bin through RvqModel::Load; dumps the device entry batch and the host entry lists
+//             for <top_n> entries per query (the argument is reused as the entry count)
+//       hpq:  dir/_hpq_outlier_pivots.bin, _hpq_codes.bin, _hpq_selector.bin (+ the base pivots); traversal on the
+//             device, then the hybrid-PQ refine; dumps the refined lists
+//       time: `repeats` passes of RunBatchFloat32Fused over the query file, prints wall and kernel times
+//     The learned traversal stop is switched on as in the reference: TOPOANNS_LEARNED_STOP_MODEL=<file> in the
+//     environment of the `search` mode.
 //   Outputs raw little-endian arrays <out_prefix>.<name>.bin (shapes are implied by the arguments).
+#include <chrono>
 #include <cstdint>
 #include <cstring>
 #include <fstream>
@@ -19,6 +27,7 @@
 #include "topoanns/entry_provider.hpp"
 #include "topoanns/pq_distance_oracle.hpp"
 #include "topoanns/rerank_exact.hpp"
+#include "topoanns/rvq_entry_provider.hpp"
 #include "topoanns/search_resources.hpp"
 #include "topoanns/topoanns_search.hpp"
 #include "topoanns/topology_search.hpp"
@@ -221,6 +230,73 @@ int main(int argc, char** argv) {
             Dump(prefix, "refined_dist", dist);
             Dump(prefix, "refined_ids", ids);
             std::cout << "traversal_kernel_ms=" << topo.kernel_ms << " pq2_refine_kernel_ms=" << refined.kernel_ms << "\n";
+        } else if (mode == "rvq") {
+            // RVQ entry selection by the reference's own RVQ::search (cuBLAS scores + its argmin kernels)
+            const std::size_t entry_count = params.rerank.top_n;
+            const RvqModel model = RvqModel::Load(dir + "/rvq_model.bin");
+            const auto lists = model.ComputeFloat32EntryPoints(queries, nq, entry_count, 0);
+            std::vector<std::uint32_t> flat(static_cast<std::size_t>(nq) * entry_count, 0xffffffffu), counts(nq);
+            for (std::uint32_t q = 0; q < nq; ++q) {
+                counts[q] = static_cast<std::uint32_t>(lists[q].size());
+                for (std::size_t i = 0; i < lists[q].size() && i < entry_count; ++i) flat[q * entry_count + i] = lists[q][i];
+            }
+            Dump(prefix, "rvq_host_ids", flat);
+            Dump(prefix, "rvq_host_counts", counts);
+            const DeviceEntryBatch dev = model.ComputeFloat32DeviceEntryBatch(queries, nq, entry_count, 0);
+            Dump(prefix, "rvq_dev_offsets", dev.offsets.CopyToHost());
+            Dump(prefix, "rvq_dev_ids", dev.ids.CopyToHost());
+        } else if (mode == "hpq") {
+            res.LoadHpqIndex(dir + "/_pq_pivots.bin", dir + "/_hpq_outlier_pivots.bin", dir + "/_hpq_codes.bin",
+                             dir + "/_hpq_selector.bin");
+            DeviceEntryBatch batch;
+            batch.num_queries = nq;
+            batch.entries_per_query = ecount;
+            std::vector<std::uint32_t> offsets(nq + 1), flat;
+            for (std::uint32_t q = 0; q <= nq; ++q) offsets[q] = q * ecount;
+            for (const auto& e : entries) flat.insert(flat.end(), e.begin(), e.end());
+            batch.offsets = CudaBuffer<std::uint32_t>::CopyFromHost(offsets);
+            batch.ids = CudaBuffer<std::uint32_t>::CopyFromHost(flat);
+            const auto oracle = PqDistanceOracle::FromFloatQueries(res, queries, nq);
+            TopologySearchParams tp = params.topology;
+            tp.candidate_queue_size = std::max(tp.top_l, params.rerank.top_n);
+            const auto topo = detail::RunTopologySearchKernelBatchDevice(res, oracle, batch, tp);
+            const CudaBuffer<float> dq = CudaBuffer<float>::CopyFromHost(queries);
+            const auto refined = detail::RunHpqRefineBatchDevice(res, topo, dq, nq, params.topology.top_l, nullptr);
+            const auto host = refined.candidate_buffer.CopyToHost();
+            std::vector<float> dist;
+            std::vector<std::uint32_t> ids;
+            for (const auto& c : host) { dist.push_back(c.distance); ids.push_back(c.node_id); }
+            Dump(prefix, "refined_dist", dist);
+            Dump(prefix, "refined_ids", ids);
+        } else if (mode == "time") {
+            // the reference's fused path (device entries given), timed as a caller sees it
+            DeviceEntryBatch batch;
+            batch.num_queries = nq;
+            batch.entries_per_query = ecount;
+            std::vector<std::uint32_t> offsets(nq + 1), flat;
+            for (std::uint32_t q = 0; q <= nq; ++q) offsets[q] = q * ecount;
+            for (const auto& e : entries) flat.insert(flat.end(), e.begin(), e.end());
+            batch.offsets = CudaBuffer<std::uint32_t>::CopyFromHost(offsets);
+            batch.ids = CudaBuffer<std::uint32_t>::CopyFromHost(flat);
+            TopoAnnsSearch::RunBatchFloat32Fused(res, batch, queries, nq, params);   // warm-up
+            double best_ms = 1e30, sum_ms = 0.0, traversal_ms = 0.0;
+            std::vector<std::uint32_t> ids;
+            for (int rep = 0; rep < repeats; ++rep) {
+                const auto t0 = std::chrono::steady_clock::now();
+                const auto out = TopoAnnsSearch::RunBatchFloat32Fused(res, batch, queries, nq, params);
+                const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+                best_ms = std::min(best_ms, ms);
+                sum_ms += ms;
+                traversal_ms = out.topology_profile.kernel_ms;
+                if (rep + 1 == repeats) {
+                    for (const auto& q : out.queries)
+                        for (std::size_t i = 0; i < params.rerank.top_k; ++i)
+                            ids.push_back(i < q.rerank.topk.size() ? q.rerank.topk[i].node_id : 0xffffffffu);
+                }
+            }
+            Dump(prefix, "time_topk_ids", ids);
+            std::cout << "ref_time queries=" << nq << " repeats=" << repeats << " best_ms=" << best_ms
+                      << " mean_ms=" << sum_ms / repeats << " traversal_kernel_ms=" << traversal_ms << "\n";
         } else {
             std::cerr << "unknown mode " << mode << "\n";
             return 2;

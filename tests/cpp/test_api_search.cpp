@@ -325,6 +325,59 @@ void TestPq2() {
     CHECK_THROWS(TopoAnnsSearch::RunBatchFloat32Fused(r, MakeEntryBatch(1, {0}), {1.0f, 1.0f}, 1, p));
 }
 
+void TestHpqIndexAndRefine() {
+    // Hybrid PQ (include/topoanns/hpq_index.hpp, src/io/hpq_index.cpp, refine src/search/rerank_exact.cu:667-771):
+    // one chunk of one dim; base table[c] = c, outlier table[c] = 100 + c; node n's hybrid code is n + 1 and the
+    // selector bit of node 1 picks the outlier codebook. Query 0: hybrid distances are node 0 -> 1^2,
+    // node 1 -> 102^2, node 2 -> 3^2, so the refined order is 0, 2, 1 although the base codes order them 0, 1, 2.
+    std::vector<float> out_tables(256);
+    for (std::size_t c = 0; c < 256; ++c) out_tables[c] = 100.0f + static_cast<float>(c);
+    fx::WritePq(fx::Tmp("hpq_base_pivots.bin"), fx::Tmp("hpq_base_codes.bin"), 1, fx::RampTables(1), {1, 2, 3});
+    fx::WritePq(fx::Tmp("hpq_outlier_pivots.bin"), fx::Tmp("hpq_codes.bin"), 1, out_tables, {1, 2, 3});
+    {
+        std::ofstream f(fx::Tmp("hpq_selector.bin"), std::ios::binary | std::ios::trunc);
+        const std::int32_t rows = 3, cols = 1;
+        const std::uint8_t bits[3] = {0, 1, 0};
+        f.write(reinterpret_cast<const char*>(&rows), 4);
+        f.write(reinterpret_cast<const char*>(&cols), 4);
+        f.write(reinterpret_cast<const char*>(bits), 3);
+    }
+    SearchResources r = SearchResources::FromDataset(TopologyLayout::MakePadded(3, {{1, 2}, {}, {}}));
+    CHECK_THROWS(r.LoadHpqIndex(fx::Tmp("hpq_base_pivots.bin"), fx::Tmp("hpq_outlier_pivots.bin"), fx::Tmp("hpq_codes.bin"),
+                                fx::Tmp("hpq_selector.bin")));   // base PQ index first
+    r.LoadPqIndex(fx::Tmp("hpq_base_pivots.bin"), fx::Tmp("hpq_base_codes.bin"));
+    CHECK_TRUE(!r.has_hpq_index());
+    CHECK_THROWS(r.hpq_index());
+    r.LoadHpqIndex(fx::Tmp("hpq_base_pivots.bin"), fx::Tmp("hpq_outlier_pivots.bin"), fx::Tmp("hpq_codes.bin"),
+                   fx::Tmp("hpq_selector.bin"));
+    CHECK_TRUE(r.has_hpq_index());
+    CHECK_EQ(r.hpq_index().selector_stride_bytes(), std::size_t{1});
+    CHECK_TRUE(r.hpq_index().outlier_index().codes_are_mapped());
+    CHECK_TRUE(r.hpq_index().device_selector_bits() != nullptr);
+    TopologySearchParams tp;
+    tp.top_k = 3; tp.top_l = 4; tp.search_width = 1; tp.max_expansions = 8;
+    const auto lists = HpqRefine::RunBatchFloat32(r, MakeEntryBatch(1, {0}), {0.0f}, 1, tp, 4);
+    CHECK_EQ(lists.size(), std::size_t{1});
+    CHECK_EQ(lists[0].size(), std::size_t{3});
+    CHECK_EQ(lists[0][0].node_id, 0u);
+    CHECK_EQ(lists[0][0].distance, 1.0f);
+    CHECK_EQ(lists[0][1].node_id, 2u);
+    CHECK_EQ(lists[0][1].distance, 9.0f);
+    CHECK_EQ(lists[0][2].node_id, 1u);
+    CHECK_EQ(lists[0][2].distance, 102.0f * 102.0f);
+    // a selector file of the wrong shape is refused
+    {
+        std::ofstream f(fx::Tmp("hpq_selector_bad.bin"), std::ios::binary | std::ios::trunc);
+        const std::int32_t rows = 2, cols = 1;
+        const std::uint8_t bits[2] = {0, 1};
+        f.write(reinterpret_cast<const char*>(&rows), 4);
+        f.write(reinterpret_cast<const char*>(&cols), 4);
+        f.write(reinterpret_cast<const char*>(bits), 2);
+    }
+    CHECK_THROWS(HpqIndex::Load(fx::Tmp("hpq_base_pivots.bin"), fx::Tmp("hpq_outlier_pivots.bin"), fx::Tmp("hpq_codes.bin"),
+                                fx::Tmp("hpq_selector_bad.bin")));
+}
+
 void TestLearnedRerankStop() {
     // Persistent rerank with the learned stop (src/io/bam_vector_provider.cu:721-1323, :2471-2774) through the
     // fused entry point. 24 nodes on a line, query at 0: node i is at i + 1 (exact distance (i + 1)^2) but its
@@ -482,6 +535,7 @@ int main() {
     TestRerankAndEndToEnd();
     TestUint8EntryPoint();
     TestPq2();
+    TestHpqIndexAndRefine();
     TestLearnedRerankStop();
     TestRvqModel();
     std::cout << "test_api_search passed" << std::endl;

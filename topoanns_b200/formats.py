@@ -220,6 +220,25 @@ def write_rvq_model(path, coarse, fine, buckets) -> None:
                 f.write(ids.tobytes())
 
 
+def write_hpq_selector_bits(path, bits) -> None:
+    """Selector-bit file of a hybrid-PQ index (src/io/hpq_index.cpp:69-86): int32 rows, int32 cols, then
+    rows x cols bytes; bit m & 7 of byte m >> 3 of a node's row picks the outlier codebook for chunk m."""
+    bits = np.ascontiguousarray(bits, np.uint8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<ii", bits.shape[0], bits.shape[1]))
+        f.write(bits.tobytes())
+
+
+def read_hpq_selector_bits(path, num_points=None, num_chunks=None):
+    raw = open(path, "rb").read()
+    rows, cols = struct.unpack_from("<ii", raw, 0)
+    if rows < 0 or cols <= 0 or len(raw) < 8 + rows * cols:
+        raise ValueError("HpqIndex::Load: Invalid selector-bit metadata.")
+    if (num_points is not None and rows != num_points) or (num_chunks is not None and cols != (num_chunks + 7) // 8):
+        raise ValueError("HpqIndex::Load: Selector-bit shape does not match HPQ codes.")
+    return np.frombuffer(raw, np.uint8, rows * cols, 8).reshape(rows, cols)
+
+
 def read_rvq_model(path):
     raw = open(path, "rb").read()
     d, nc, nf = struct.unpack_from("<iii", raw, 0)

@@ -238,6 +238,59 @@ PqIndex PqIndex::LoadFromSeparatePaths(const std::filesystem::path& p, const std
 PqIndex PqIndex::LoadFromSeparatePathsMapped(const std::filesystem::path& p, const std::filesystem::path& c) { return LoadImpl(p, c, true, true); }
 PqIndex PqIndex::LoadPivotsOnly(const std::filesystem::path& p, const std::filesystem::path& c) { return LoadImpl(p, c, false, false); }
 
+// ---- hybrid PQ index (src/io/hpq_index.cpp) ---------------------------------------------------------------------
+HpqIndex::~HpqIndex() { Release(); }
+HpqIndex::HpqIndex(HpqIndex&& other) noexcept { *this = std::move(other); }
+HpqIndex& HpqIndex::operator=(HpqIndex&& other) noexcept {
+    if (this != &other) {
+        Release();
+        base_index_ = std::move(other.base_index_);
+        outlier_index_ = std::move(other.outlier_index_);
+        selector_stride_bytes_ = other.selector_stride_bytes_;
+        mapped_host_selector_bits_ = other.mapped_host_selector_bits_;
+        mapped_device_selector_bits_ = other.mapped_device_selector_bits_;
+        other.selector_stride_bytes_ = 0;
+        other.mapped_host_selector_bits_ = nullptr;
+        other.mapped_device_selector_bits_ = nullptr;
+    }
+    return *this;
+}
+void HpqIndex::Release() noexcept {
+    if (mapped_host_selector_bits_ != nullptr) tann_host_free(mapped_host_selector_bits_);
+    mapped_host_selector_bits_ = nullptr;
+    mapped_device_selector_bits_ = nullptr;
+    selector_stride_bytes_ = 0;
+}
+HpqIndex HpqIndex::Load(const std::filesystem::path& base_pivots_path, const std::filesystem::path& outlier_pivots_path,
+                        const std::filesystem::path& hybrid_codes_path, const std::filesystem::path& selector_bits_path) {
+    const char* ctx = "HpqIndex::Load";
+    HpqIndex result;
+    result.base_index_ = PqIndex::LoadPivotsOnly(base_pivots_path, hybrid_codes_path);
+    result.outlier_index_ = PqIndex::LoadFromSeparatePathsMapped(outlier_pivots_path, hybrid_codes_path);
+    std::ifstream in(selector_bits_path, std::ios::binary);
+    std::int32_t rows = 0, cols = 0;
+    in.read(reinterpret_cast<char*>(&rows), sizeof(rows));
+    in.read(reinterpret_cast<char*>(&cols), sizeof(cols));
+    if (!in.good() || rows < 0 || cols <= 0) throw std::runtime_error(BuildErrorMessage(ctx, "Invalid selector-bit metadata."));
+    const auto& host = result.outlier_index_.host();
+    const std::size_t stride = (host.num_chunks + 7U) / 8U;
+    if (static_cast<std::uint64_t>(rows) != host.num_points || static_cast<std::size_t>(cols) != stride)
+        throw std::runtime_error(BuildErrorMessage(ctx, "Selector-bit shape does not match HPQ codes."));
+    const std::size_t total = static_cast<std::size_t>(rows) * stride;
+    void* hp = nullptr;
+    void* dp = nullptr;
+    ThrowIfTannError(tann_host_alloc_mapped(total == 0 ? 16 : total, &hp, &dp), ctx);
+    result.mapped_host_selector_bits_ = static_cast<std::uint8_t*>(hp);
+    result.mapped_device_selector_bits_ = static_cast<std::uint8_t*>(dp);
+    result.selector_stride_bytes_ = stride;
+    in.read(reinterpret_cast<char*>(result.mapped_host_selector_bits_), static_cast<std::streamsize>(total));
+    if (static_cast<std::size_t>(in.gcount()) != total) {
+        result.Release();
+        throw std::runtime_error(BuildErrorMessage(ctx, "Short selector-bit read."));
+    }
+    return result;
+}
+
 // ---- providers ----------------------------------------------------------------------------------------------
 DevicePageReadResult VectorPageProvider::ReadPagesToDevice(const std::filesystem::path&, const std::vector<std::uint64_t>&,
                                                            std::size_t, std::size_t) const {
@@ -360,6 +413,23 @@ void SearchResources::LoadPq2Index(const std::filesystem::path& pivots, const st
 const PqIndex& SearchResources::pq2_index() const {
     if (!pq2_index_) throw std::runtime_error(BuildErrorMessage("SearchResources::pq2_index", "PQ2 index is not loaded."));
     return *pq2_index_;
+}
+void SearchResources::LoadHpqIndex(const std::filesystem::path& base_pivots_path, const std::filesystem::path& outlier_pivots_path,
+                                   const std::filesystem::path& hybrid_codes_path, const std::filesystem::path& selector_bits_path) {
+    // src/search/search_resources.cpp:221-246
+    const char* ctx = "SearchResources::LoadHpqIndex";
+    if (!pq_index_) throw std::runtime_error(BuildErrorMessage(ctx, "Base PQ index must be loaded first."));
+    auto hpq = std::make_shared<HpqIndex>(HpqIndex::Load(base_pivots_path, outlier_pivots_path, hybrid_codes_path, selector_bits_path));
+    const auto& base = hpq->base_index().host();
+    const auto& outlier = hpq->outlier_index().host();
+    if (base.ndims != outlier.ndims || base.num_chunks != outlier.num_chunks || base.chunk_offsets != outlier.chunk_offsets)
+        throw std::runtime_error(BuildErrorMessage(ctx, "Base and outlier HPQ layouts differ."));
+    if (outlier.num_points != num_nodes()) throw std::runtime_error(BuildErrorMessage(ctx, "Graph and HPQ dataset shapes differ."));
+    hpq_index_ = std::move(hpq);
+}
+const HpqIndex& SearchResources::hpq_index() const {
+    if (!hpq_index_) throw std::runtime_error(BuildErrorMessage("SearchResources::hpq_index", "HPQ index is not loaded."));
+    return *hpq_index_;
 }
 bool SearchResources::pq2_is_residual_refine() const { return pq2_aux_ && pq2_aux_->residual_refine; }
 bool SearchResources::has_pq2_error_bounds() const { return pq2_aux_ && pq2_aux_->storage != Pq2ErrorBoundStorage::kNone; }

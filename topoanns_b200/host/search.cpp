@@ -974,6 +974,54 @@ std::vector<TopologySearchResult> TopologySearch::RunBatch(const SearchResources
                        params, profile);
 }
 
+// ---- HpqRefine (src/search/rerank_exact.cu:2457-2531) --------------------------------------------------------------
+std::vector<std::vector<RankedCandidate>> HpqRefine::RunBatchFloat32(const SearchResources& resources,
+                                                                     const DeviceEntryBatch& batch,
+                                                                     const std::vector<float>& queries, std::size_t num_queries,
+                                                                     const TopologySearchParams& params, std::size_t refine_top_l) {
+    const char* ctx = "RunHpqRefineBatchDevice";
+    ValidateTopologyParams(params, ctx);
+    if (!resources.has_hpq_index()) throw std::runtime_error(BuildErrorMessage(ctx, "HPQ index must be loaded."));
+    if (batch.num_queries != num_queries) throw std::runtime_error(BuildErrorMessage(ctx, "topology_result size mismatch."));
+    std::vector<std::vector<RankedCandidate>> out(num_queries);
+    if (num_queries == 0 || refine_top_l == 0) return out;
+    const HpqIndex& hpq = resources.hpq_index();
+    const PqIndex& base = hpq.base_index();
+    const PqIndex& outlier = hpq.outlier_index();
+    const std::uint32_t M = static_cast<std::uint32_t>(outlier.host().num_chunks);
+    const std::uint32_t dim = static_cast<std::uint32_t>(outlier.host().ndims);
+    if (queries.size() != num_queries * dim) throw std::runtime_error(BuildErrorMessage(ctx, "queries size must equal num_queries * dim."));
+    const CudaBuffer<float> d_queries = CudaBuffer<float>::CopyFromHost(queries);
+    const DeviceTraversal topo = RunTraversal(resources, params, nullptr, d_queries.get(), TANN_KIND_FLOAT32, num_queries,
+                                              batch.offsets.get(), batch.ids.get());
+    if (refine_top_l > topo.capacity || refine_top_l > 2048)
+        throw std::runtime_error(BuildErrorMessage(ctx, "HPQ refine size exceeds candidate limits."));
+    CudaBuffer<float> base_lut = CudaBuffer<float>::Allocate(num_queries * M * kNumPqCentroids);
+    CudaBuffer<float> outlier_lut = CudaBuffer<float>::Allocate(num_queries * M * kNumPqCentroids);
+    ThrowIfTannError(tann_lut_build(base.device().tables_col_major.get(), base.device().centroid.get(),
+                                    base.device().chunk_offsets.get(), dim, M, d_queries.get(), TANN_KIND_FLOAT32, num_queries,
+                                    base_lut.get(), nullptr), ctx);
+    ThrowIfTannError(tann_lut_build(outlier.device().tables_col_major.get(), outlier.device().centroid.get(),
+                                    outlier.device().chunk_offsets.get(), dim, M, d_queries.get(), TANN_KIND_FLOAT32, num_queries,
+                                    outlier_lut.get(), nullptr), ctx);
+    CudaBuffer<DeviceCand> refined = CudaBuffer<DeviceCand>::Allocate(num_queries * refine_top_l);
+    TannShards codes{};
+    codes.num_shards = 1;
+    codes.base[0] = outlier.device_codes();
+    ThrowIfTannError(tann_hpq_refine(topo.candidates.get(), topo.stats.get(), num_queries, topo.capacity,
+                                     static_cast<std::uint32_t>(refine_top_l), &codes, hpq.device_selector_bits(), M,
+                                     base_lut.get(), outlier_lut.get(), refined.get(), nullptr, nullptr), ctx);
+    ThrowIfCudaError(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    const std::vector<DeviceCand> host = refined.CopyToHost();
+    for (std::size_t q = 0; q < num_queries; ++q)
+        for (std::size_t i = 0; i < refine_top_l; ++i) {
+            const DeviceCand& c = host[q * refine_top_l + i];
+            if (c.node_id == kInvalidNodeId) continue;
+            out[q].push_back(RankedCandidate{c.distance, c.node_id & ~kExpandedBit, false});
+        }
+    return out;
+}
+
 // ---- RerankExact -----------------------------------------------------------------------------------------------------
 RerankBatchResult RerankExact::RunBatchFloat32(const SearchResources& r, const std::vector<TopologySearchResult>& topo,
                                                const std::vector<float>& q, std::size_t n, const RerankExactParams& p,

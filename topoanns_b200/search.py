@@ -64,6 +64,58 @@ class TopologySearchParams:
         return p
 
 
+def load_learned_stop(path, top_l: int, top_k: int, shadow: bool = False) -> capi.LearnedStop:
+    """Reads a learned traversal-stop model file (`key = value` lines: stage_prefixes, feature_means,
+    feature_inv_stds, weights, bias, threshold_logit, top_k, topk_churn_mode, next64_mode, feature_mask,
+    threshold_logit_top_l_<L>) and folds it for one top_l the way the reference does
+    (src/search/topology_search_kernel.cu:248-380): weight_i / std_i per feature, the means folded into the bias,
+    stages outside (0, top_l) dropped, the per-top_l threshold preferred."""
+    vals = {}
+    with open(path) as f:
+        for line in f:
+            line = line.strip()
+            if not line or line.startswith("#"):
+                continue
+            if "=" not in line:
+                raise ValueError("LoadLearnedStopConfigFromFile: Invalid learned-stop config line: " + line)
+            k, v = line.split("=", 1)
+            vals[k.strip()] = v.strip()
+
+    def floats(key):
+        return [np.float32(x) for x in vals.get(key, "").split(",") if x.strip()]
+
+    means, inv_stds, weights = floats("feature_means"), floats("feature_inv_stds"), floats("weights")
+    if not (len(means) == len(inv_stds) == len(weights) == 12):
+        raise ValueError("LoadLearnedStopConfigFromFile: learned-stop feature vectors must all have length 12.")
+    mask = [int(x) for x in vals.get("feature_mask", "").split(",") if x.strip()]
+    ls = capi.LearnedStop()
+    ls.top_k = int(vals.get("top_k", "0")) or top_k
+    ls.inv_top_l = float(np.float32(1.0) / np.float32(top_l)) if top_l else 0.0
+    ls.shadow_mode = int(shadow)
+    ls.topk_churn_flag_mode = int(vals.get("topk_churn_mode", "") == "flag")
+    ls.next64_flag_mode = int(vals.get("next64_mode", "") == "flag")
+    key = f"threshold_logit_top_l_{top_l}"
+    ls.threshold_logit = float(np.float32(vals[key] if key in vals else vals.get("threshold_logit", "0")))
+    bias = np.float32(vals.get("bias", "0"))
+    for i in range(12):
+        ls.feature_mask[i] = mask[i] if i < len(mask) else 1
+        w = (weights[i] if ls.feature_mask[i] else np.float32(0.0)) * inv_stds[i]
+        ls.weights[i] = float(w)
+        bias = np.float32(bias - means[i] * w)
+    ls.bias = float(bias)
+    n = 0
+    for pfx in (int(x) for x in vals.get("stage_prefixes", "").split(",") if x.strip()):
+        if pfx == 0 or pfx >= top_l:
+            continue
+        if n >= 32:
+            break
+        ls.stage_prefixes[n] = pfx
+        n += 1
+    ls.num_stages = n
+    ls.enabled = int(n > 0 and 0 < ls.top_k <= 32)
+    return ls
+
+
 @dataclass
 class RerankExactParams:
     """include/topoanns/rerank_exact.hpp:21-37 (the fields this path uses)."""
