@@ -69,6 +69,8 @@ def parse_args():
     ap.add_argument("--top-n", type=int, default=0, help="with --top-l: rerank top_n (default 32)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="--impl reference: skip the timed run of the reference's own GPU kernels (oracle/_ref)")
     ap.add_argument("--streams", type=int, default=4,
                     help="searchers (each on its own stream) that the steps alternate between; 1 = one batch at a time")
     ap.add_argument("--no-neighbor-codes", action="store_true",
@@ -78,6 +80,7 @@ def parse_args():
     ap.add_argument("--no-sharded-leg", action="store_true", help="N > 1: skip the node-id-range-sharded leg")
     ap.add_argument("--stages", action="store_true",
                     help="per-stage CUDA-event timings of one synthetic case (1 GPU), one line per stage; for profilers")
+    ap.add_argument("--top-l-values", default="", help="--stages: comma-separated top_l values timed on one index build")
     ap.add_argument("--search-width", type=int, default=2)
     ap.add_argument("--entries", type=int, default=128)
     ap.add_argument("--reps", type=int, default=5, help="--stages: timed calls per stage")
@@ -86,6 +89,7 @@ def parse_args():
                     help="--stages: where the adjacency lists live (pinned-host = mapped host memory read over PCIe)")
     ap.add_argument("--vectors", default="hbm", choices=["hbm", "pinned-host"],
                     help="--stages: where the vector pages live")
+    ap.add_argument("--cached-fractions", default="", help="--stages: comma-separated cached fractions timed on one index build")
     ap.add_argument("--cached-fraction", type=float, default=0.0,
                     help="--stages --topology pinned-host: fraction of the rows (an id prefix) cached in HBM")
     return ap.parse_args()
@@ -218,9 +222,54 @@ def cpu_leg(s, L, top_n, seconds, cuda_ids=None, cuda_dists=None):
     return res, parity
 
 
+def reference_gpu_leg(s, host, L, top_n, cpu_ids=None):
+    """The reference's own CUDA kernels (its sources compiled in place for sm_100a by oracle/ref_build.sh) on the
+    same index, queries and parameters, beside the CPU baseline: its fused entry point RunBatchFloat32Fused with
+    the entry lists given, timed per batch as a caller sees it (its query upload, kernels, result download and
+    host materialisation). Returns None when that build or a GPU is absent."""
+    driver = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
+    if not (os.path.exists(driver) and torch.cuda.is_available()) or host["adjacency"].shape[1] > 64:
+        return None
+    from oracle import oracle as orc
+    from topoanns_b200 import formats
+    q = s.queries.cpu().numpy()
+    with tempfile.TemporaryDirectory() as tmp:
+        formats.write_topology(os.path.join(tmp, "topology.bin"), formats.pad_degree(host["adjacency"], 64))
+        formats.write_pq(os.path.join(tmp, "_pq_pivots.bin"), os.path.join(tmp, "_pq_compressed.bin"), host["pq_tables"],
+                         host["pq_centroid"], host["pq_chunk_offsets"], host["codes"])
+        formats.write_vector_store(os.path.join(tmp, "vectors.ssd"), host["vectors"])
+        formats.write_fbin(os.path.join(tmp, "queries.fbin"), q)
+        clusters, _, _ = orc.rvq_clusters(q, host["rvq_coarse"], host["rvq_fine"], host["rvq_sizes"])
+        entries = np.ascontiguousarray(orc.rvq_gather(clusters, host["rvq_offsets"], host["rvq_ids"], 128), np.uint32)
+        with open(os.path.join(tmp, "entries.bin"), "wb") as f:
+            f.write(np.array(entries.shape, np.uint32).tobytes())
+            f.write(entries.tobytes())
+        r = subprocess.run([driver, tmp, os.path.join(tmp, "out"), "time", str(L), "2", "4096", "10", str(top_n), "linear",
+                            "16", "0", "0", "3"], capture_output=True, text=True, timeout=1200)
+        if r.returncode != 0:
+            return {"error": (r.stdout + r.stderr)[-300:]}
+        fields = {}
+        for line in r.stdout.splitlines():
+            if line.startswith("ref_time"):
+                fields = dict(kv.split("=") for kv in line.split()[1:])
+        ids = np.fromfile(os.path.join(tmp, "out.time_topk_ids.bin"), np.uint32).reshape(q.shape[0], 10)
+    from topoanns_b200 import synth
+    out = {"value": q.shape[0] / (float(fields["best_ms"]) * 1e-3), "unit": "queries/s",
+           "ms_per_batch": float(fields["best_ms"]), "traversal_kernel_ms": float(fields["traversal_kernel_ms"]),
+           "recall_at_10": round(synth.recall_at_k(ids, s.gt_ids.cpu().numpy(), 10), 4),
+           "what": "the reference's CUDA kernels compiled in place for sm_100a, RunBatchFloat32Fused on the same index files "
+                   f"({q.shape[0]} queries, top_l={L}, rerank_top_n={top_n}, linear rerank, entry lists given), best of 3 batches, "
+                   "wall clock around the call; RVQ entry selection is not in its timed call and its persistent rerank "
+                   "needs the NVMe provider"}
+    if cpu_ids is not None:
+        n = min(cpu_ids.shape[0], ids.shape[0])
+        out["top10_identical_to_cpu_port_frac"] = float((ids[:n] == cpu_ids[:n]).all(1).mean())
+    return out
+
+
 def reference_arm(args, s, workload):
     """The reference's path on the host cores (CPU restatement; the reference ships no CPU implementation of the
-    batched path of its own and its GPU kernels are not a CPU baseline)."""
+    batched path of its own), and beside it - one GPU, first rank only - the reference's own GPU kernels."""
     Q = s.queries.shape[0]
     L = args.top_l or DEFAULT_POINT[0]       # the operating point the CUDA arm's sweep settles on for this seeded workload
     top_n = args.top_n or DEFAULT_POINT[1]
@@ -233,6 +282,14 @@ def reference_arm(args, s, workload):
                        "note": "host cores only; one process whatever --gpus says"},
             "cpu_baseline": res,
             "e2e": {"value": res["value"], "unit": "queries/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if args.gpus == 1 and not args.no_reference_gpu:
+        try:
+            from oracle import pipeline
+            rg = reference_gpu_leg(s, pipeline.index_from_synth(s), L, top_n)
+            if rg is not None:
+                line["reference_gpu"] = rg
+        except Exception as e:   # an aid beside the baseline: never takes the line down
+            line["reference_gpu"] = {"error": f"{type(e).__name__}: {e}"}
     print(json.dumps(line))
 
 
@@ -251,21 +308,21 @@ def _time_calls(fn, reps):
 
 def stage_timings(args):
     """The stages of the path, each timed alone with CUDA events on one synthetic case (any configuration, any
-    size); prints one line per stage and a closing JSON line. Small cases of this mode are what profiler
-    captures run."""
+    size); prints one line per stage and a closing JSON line per case. Small cases of this mode are what profiler
+    captures run. One index build serves every value of --top-l-values and --cached-fractions."""
     from topoanns_b200 import capi, search, synth
     lib = capi.load()
     s, build_s = build_index(args, "cuda")
     cfg = s.cfg
-    ix = search.device_index_from_synth(s)
+    base_ix = search.device_index_from_synth(s)
     q = s.queries.cuda().contiguous()
     Qn = q.shape[0]
-    out = {"config": args.config, "nodes": int(s.vectors.shape[0]), "queries": Qn, "top_l": args.top_l or 64,
-           "top_n": args.top_n or 32, "index_build_s": round(build_s, 1), "stages_ms": {}}
-    top_l, top_n = out["top_l"], out["top_n"]
-    if not args.no_neighbor_codes and args.topology == "hbm" and ix.num_nodes * ix.degree * ix.num_chunks <= 40e9:
-        search.inline_neighbor_codes(ix)
-        print(f"neighbour-code layout: {ix.neighbor_codes.numel() / 1e9:.2f} GB")
+    top_n = args.top_n or 32
+    top_ls = [int(x) for x in args.top_l_values.split(",") if x] or [args.top_l or 64]
+    gt = s.gt_ids.cpu().numpy()
+    if not args.no_neighbor_codes and args.topology == "hbm" and base_ix.num_nodes * base_ix.degree * base_ix.num_chunks <= 40e9:
+        search.inline_neighbor_codes(base_ix)
+        print(f"neighbour-code layout: {base_ix.neighbor_codes.numel() / 1e9:.2f} GB")
     host_allocs = []
 
     def to_mapped_host(t):
@@ -280,128 +337,152 @@ def stage_timings(args):
             C.memmove(hp.value + b, part.ctypes.data, part.nbytes)
         return dp.value, nbytes
 
-    if args.topology == "pinned-host" or args.vectors == "pinned-host":
-        kw = dict(num_nodes=ix.num_nodes, degree=ix.degree, dim=ix.dim, vector_kind=ix.vector_kind, codes=ix.codes,
-                  pq_tables_col_major=ix.pq_tables_col_major, pq_centroid=ix.pq_centroid,
-                  pq_chunk_offsets=ix.pq_chunk_offsets, vector_bytes=ix.vector_bytes,
-                  vectors_per_page=ix.vectors_per_page)
-        if args.topology == "pinned-host":
-            dp, nbytes = to_mapped_host(ix.adjacency)
-            cached = int(ix.num_nodes * args.cached_fraction)
-            kw.update(adjacency_bases=[dp], adjacency_cache=ix.adjacency[:cached].clone() if cached else None,
-                      adjacency_cached_rows=cached)
-            print(f"topology: {nbytes / 1e9:.2f} GB in mapped pinned host memory, {cached} rows "
-                  f"({args.cached_fraction:.0%}) cached in HBM")
-        else:
-            kw.update(adjacency=ix.adjacency)
-        if args.vectors == "pinned-host":
-            dp, nbytes = to_mapped_host(ix.vector_pages)
-            kw.update(vector_bases=[dp])
-            print(f"vector pages: {nbytes / 1e9:.2f} GB in mapped pinned host memory")
-        else:
-            kw.update(vector_pages=ix.vector_pages)
-        ix = search.DeviceIndex(**kw)
-    if cfg.rvq:
-        model = search.rvq_model_from_synth(s)
-        (offs, ids, _), ms = _time_calls(lambda: model.device_entry_batch(q, args.entries), args.reps)
-        out["stages_ms"]["rvq_entries"] = ms
-        print(f"rvq_entries {ms:.3f} ms")
-    else:
-        offs = torch.arange(Qn + 1, dtype=torch.int32, device="cuda")
-        ids = torch.full((Qn,), int(s.medoid), dtype=torch.int32, device="cuda")
-    p = search.TopologySearchParams(top_l=top_l, search_width=args.search_width, max_expansions=4096)
-    cap = p.capacity(top_n)
-    lut = None
-    if args.staged_table:
-        lut, ms = _time_calls(lambda: search.lut_build(ix, q), args.reps)
-        out["stages_ms"]["lut_build"] = ms
-        print(f"lut_build {ms:.3f} ms")
-    (cand, stats), ms = _time_calls(lambda: search.beam_search(ix, p, offs, ids, queries=None if lut is not None else q,
-                                                               lut=lut, capacity=cap), args.reps)
-    st = stats.cpu().numpy()
-    e, v = float(st[:, 1].mean()), float(st[:, 0].mean())
-    gbytes = Qn * (e * 4 * ix.degree + v * ix.num_chunks) / 1e9
-    smem, bps, _ = search.beam_occupancy(ix, p, cap)
-    out["stages_ms"]["beam_search"] = ms
-    out["beam"] = dict(expanded=e, visited=v, algorithmic_gb=gbytes, gbs=gbytes / ms * 1e3, smem_bytes=smem, blocks_per_sm=bps)
-    print(f"beam_search {ms:.3f} ms  nodes={ix.num_nodes} queries={Qn} L={top_l} C={cap} expanded/query={e:.1f} "
-          f"visited/query={v:.1f} algorithmic={gbytes:.3f} GB -> {gbytes / ms * 1e3:.1f} GB/s  ({bps} blocks/SM, {smem} B smem)")
-    rp = search.RerankExactParams(top_k=10, top_n=top_n)
-    (_, rr_ids, _, _), ms = _time_calls(lambda: search.rerank_exact(ix, rp, cand, q), args.reps)
-    gb = Qn * top_n * ix.vector_bytes / 1e9
-    out["stages_ms"]["rerank_exact_f32_queries"] = ms
-    out["recall_at_10"] = round(synth.recall_at_k(rr_ids.cpu().numpy().view(np.uint32), s.gt_ids.cpu().numpy(), 10), 4)
-    print(f"rerank_exact {ms:.3f} ms  top_n={top_n}  (float32 queries) {gb / ms * 1e3:.1f} GB/s  recall@10={out['recall_at_10']}")
-    if s.vectors.dtype == torch.uint8:
-        q8 = q.to(torch.uint8).contiguous()   # the searcher makes this copy on the device when the values allow it
-        _, ms = _time_calls(lambda: search.rerank_exact(ix, rp, cand, q8), args.reps)
-        out["stages_ms"]["rerank_exact_u8_queries"] = ms
-        print(f"rerank_exact {ms:.3f} ms  top_n={top_n}  (uint8 queries, integer path) {gb / ms * 1e3:.1f} GB/s")
-    if cfg.rvq and s.pq2_tables is None:
-        sr = search.Searcher(ix, Qn, cap, top_n, args.entries)
-        sr.set_rvq(model, args.entries)
-        _, ms = _time_calls(lambda: sr.run_device(q, p, rp), args.reps)
-        out["stages_ms"]["searcher_whole_path"] = ms
-        out["qps_whole_path"] = Qn / ms * 1e3
-        print(f"searcher whole path (rvq, beam, rerank, top-k) {ms:.3f} ms = {Qn / ms * 1e3:.0f} queries/s")
-        sr.close()
+    adj_mapped = vec_mapped = None
+    if args.topology == "pinned-host":
+        adj_mapped, nbytes = to_mapped_host(base_ix.adjacency)
+        print(f"topology: {nbytes / 1e9:.2f} GB in mapped pinned host memory")
+    if args.vectors == "pinned-host":
+        vec_mapped, nbytes = to_mapped_host(base_ix.vector_pages)
+        print(f"vector pages: {nbytes / 1e9:.2f} GB in mapped pinned host memory")
+        base_ix.vector_pages = None    # the HBM copy is not needed any more
+        torch.cuda.empty_cache()
+    model = search.rvq_model_from_synth(s) if cfg.rvq else None
+    pq2 = None
     if s.pq2_tables is not None:
-        # residual pq2 refine + bound filter (float configurations): second table build, refine, tiled rerank
         t2 = s.pq2_tables.cuda().contiguous()
-        c2 = s.pq2_centroid.cuda().contiguous()
-        codes2 = s.pq2_codes.cuda().contiguous()
-        cross = search.pq2_cross_terms(ix.pq_chunk_offsets, s.pq_tables.cuda().contiguous(), ix.pq_centroid, t2, c2)
-        t2_cm = t2.t().contiguous()
-        if Qn * ix.num_chunks * 1024 <= 2e9:
-            lut2, ms = _time_calls(lambda: search.lut_build(ix, q, tables_col_major=t2_cm, centroid=c2), args.reps)
-            out["stages_ms"]["lut_build_pq2"] = ms
-            print(f"lut_build (pq2) {ms:.3f} ms  {lut2.numel() * 4 / 1e6:.0f} MB written")
-            lr = min(top_l, cap)
-            refined, ms = _time_calls(lambda: search.pq2_refine(cand, stats, lr, codes2, lut2, base_codes=ix.codes,
-                                                                cross_terms=cross), args.reps)
-            out["stages_ms"]["pq2_refine"] = ms
-            print(f"pq2_refine {ms:.3f} ms  refine_top_l={lr}")
-            eps = s.pq2_error_bounds.cuda().contiguous()
-            rp2 = search.RerankExactParams(top_k=10, top_n=min(top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
-            (_, _, n_exact, n_flt), ms = _time_calls(lambda: search.rerank_exact(ix, rp2, refined, q, eps), args.reps)
-            out["stages_ms"]["rerank_exact_tiled_bound_filter"] = ms
-            print(f"rerank_exact (tiled, bound filter) {ms:.3f} ms  exact={n_exact} filtered={n_flt}")
-            # persistent rerank with a learned stop: a synthetic model on the share of ranks scored and the top-k
-            # churn (logit = 1 - 2.5 * prefix / budget + entered / k, threshold 0)
-            ls = capi.RerankLearnedStop()
-            budget = rp2.top_n
-            stages = [pfx for pfx in (16, 32, 48, 64, 96, 128, 192, 256, 384, 512) if pfx < budget]
-            ls.enabled, ls.num_stages, ls.top_k, ls.bootstrap_prefix = 1, len(stages), 10, 16
-            for i, pfx in enumerate(stages):
-                ls.stage_prefixes[i] = pfx
-            while ls.initial_stage_index < ls.num_stages and ls.stage_prefixes[ls.initial_stage_index] <= 16:
-                ls.initial_stage_index += 1
-            ls.linear_weights[1], ls.linear_weights[6], ls.bias, ls.threshold_logit = -2.5, 1.0, 1.0, 0.0
-            ls.inv_budget_top_n, ls.inv_top_k = 1.0 / budget, 0.1
-            if ls.initial_stage_index < ls.num_stages:
-                res, ms = _time_calls(lambda: search.rerank_exact_learned_stop(ix, rp2, refined, q, model=ls,
-                                                                               error_bounds=eps), args.reps)
-                out["stages_ms"]["rerank_exact_learned_stop"] = ms
-                print(f"rerank_exact_learned_stop {ms:.3f} ms  exact={res['n_exact']} filtered={res['n_filtered']} "
-                      f"mean_stop_prefix={float(res['stop_prefixes'].float().mean()):.1f} of {budget}")
-        if cfg.rvq:
-            lr = min(top_l, cap)
-            eps = s.pq2_error_bounds.cuda().contiguous()
-            rp2 = search.RerankExactParams(top_k=10, top_n=min(top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
-            sr = search.Searcher(ix, Qn, cap, min(top_n, lr), args.entries)
+        pq2 = dict(t2=t2, c2=s.pq2_centroid.cuda().contiguous(), codes2=s.pq2_codes.cuda().contiguous(), t2_cm=t2.t().contiguous(),
+                   eps=s.pq2_error_bounds.cuda().contiguous())
+        pq2["cross"] = search.pq2_cross_terms(base_ix.pq_chunk_offsets, s.pq_tables.cuda().contiguous(), base_ix.pq_centroid,
+                                              t2, pq2["c2"])
+
+    def time_case(ix, top_l, label):
+        out = {"config": args.config, "nodes": int(ix.num_nodes), "queries": Qn, "top_l": top_l, "top_n": top_n,
+               "residency": label, "index_build_s": round(build_s, 1), "stages_ms": {}}
+        if model is not None:
+            (offs, ids, _), ms = _time_calls(lambda: model.device_entry_batch(q, args.entries), args.reps)
+            out["stages_ms"]["rvq_entries"] = ms
+            print(f"rvq_entries {ms:.3f} ms")
+        else:
+            offs = torch.arange(Qn + 1, dtype=torch.int32, device="cuda")
+            ids = torch.full((Qn,), int(s.medoid), dtype=torch.int32, device="cuda")
+        p = search.TopologySearchParams(top_l=top_l, search_width=args.search_width, max_expansions=4096)
+        cap = p.capacity(top_n)
+        lut = None
+        if args.staged_table:
+            lut, ms = _time_calls(lambda: search.lut_build(ix, q), args.reps)
+            out["stages_ms"]["lut_build"] = ms
+            print(f"lut_build {ms:.3f} ms")
+        (cand, stats), ms = _time_calls(lambda: search.beam_search(ix, p, offs, ids, queries=None if lut is not None else q,
+                                                                   lut=lut, capacity=cap), args.reps)
+        st = stats.cpu().numpy()
+        e, v = float(st[:, 1].mean()), float(st[:, 0].mean())
+        gbytes = Qn * (e * 4 * ix.degree + v * ix.num_chunks) / 1e9
+        smem, bps, _ = search.beam_occupancy(ix, p, cap)
+        out["stages_ms"]["beam_search"] = ms
+        out["beam"] = dict(expanded=e, visited=v, algorithmic_gb=gbytes, gbs=gbytes / ms * 1e3, smem_bytes=smem, blocks_per_sm=bps)
+        print(f"beam_search {ms:.3f} ms  nodes={ix.num_nodes} queries={Qn} L={top_l} C={cap} expanded/query={e:.1f} "
+              f"visited/query={v:.1f} algorithmic={gbytes:.3f} GB -> {gbytes / ms * 1e3:.1f} GB/s  ({bps} blocks/SM, {smem} B smem)")
+        rp = search.RerankExactParams(top_k=10, top_n=top_n)
+        (_, rr_ids, _, _), ms = _time_calls(lambda: search.rerank_exact(ix, rp, cand, q), args.reps)
+        gb = Qn * top_n * ix.vector_bytes / 1e9
+        out["stages_ms"]["rerank_exact_f32_queries"] = ms
+        out["recall_at_10"] = round(synth.recall_at_k(rr_ids.cpu().numpy().view(np.uint32), gt, 10), 4)
+        print(f"rerank_exact {ms:.3f} ms  top_n={top_n}  (float32 queries) {gb / ms * 1e3:.1f} GB/s  recall@10={out['recall_at_10']}")
+        if s.vectors.dtype == torch.uint8:
+            q8 = q.to(torch.uint8).contiguous()   # the searcher makes this copy on the device when the values allow it
+            _, ms = _time_calls(lambda: search.rerank_exact(ix, rp, cand, q8), args.reps)
+            out["stages_ms"]["rerank_exact_u8_queries"] = ms
+            print(f"rerank_exact {ms:.3f} ms  top_n={top_n}  (uint8 queries, integer path) {gb / ms * 1e3:.1f} GB/s")
+        if model is not None and pq2 is None:
+            sr = search.Searcher(ix, Qn, cap, top_n, args.entries)
             sr.set_rvq(model, args.entries)
-            sr.set_pq2(search.Pq2Resources(codes=codes2, tables_col_major=t2_cm, centroid=c2, chunk_offsets=ix.pq_chunk_offsets,
-                                           cross_terms=cross, error_bounds=eps), lr)
-            _, ms = _time_calls(lambda: sr.run_device(q, p, rp2), args.reps)
+            _, ms = _time_calls(lambda: sr.run_device(q, p, rp), args.reps)
             out["stages_ms"]["searcher_whole_path"] = ms
             out["qps_whole_path"] = Qn / ms * 1e3
-            print(f"searcher whole path (rvq, beam, table-free pq2 refine, bound-filtered rerank, top-k) {ms:.3f} ms "
-                  f"= {Qn / ms * 1e3:.0f} queries/s")
+            print(f"searcher whole path (rvq, beam, rerank, top-k) {ms:.3f} ms = {Qn / ms * 1e3:.0f} queries/s")
             sr.close()
+        if pq2 is not None:
+            # residual pq2 refine + bound filter (float configurations): second table build, refine, tiled rerank
+            lr = min(top_l, cap)
+            rp2 = search.RerankExactParams(top_k=10, top_n=min(top_n, lr), rank_tile_size=16, use_pq2_bound_filter=True)
+            if Qn * ix.num_chunks * 1024 <= 2e9:
+                lut2, ms = _time_calls(lambda: search.lut_build(ix, q, tables_col_major=pq2["t2_cm"], centroid=pq2["c2"]), args.reps)
+                out["stages_ms"]["lut_build_pq2"] = ms
+                print(f"lut_build (pq2) {ms:.3f} ms  {lut2.numel() * 4 / 1e6:.0f} MB written")
+                refined, ms = _time_calls(lambda: search.pq2_refine(cand, stats, lr, pq2["codes2"], lut2, base_codes=ix.codes,
+                                                                    cross_terms=pq2["cross"]), args.reps)
+                out["stages_ms"]["pq2_refine"] = ms
+                print(f"pq2_refine {ms:.3f} ms  refine_top_l={lr}")
+                (_, _, n_exact, n_flt), ms = _time_calls(lambda: search.rerank_exact(ix, rp2, refined, q, pq2["eps"]), args.reps)
+                out["stages_ms"]["rerank_exact_tiled_bound_filter"] = ms
+                print(f"rerank_exact (tiled, bound filter) {ms:.3f} ms  exact={n_exact} filtered={n_flt}")
+                # persistent rerank with a learned stop: a synthetic model on the share of ranks scored and the top-k
+                # churn (logit = 1 - 2.5 * prefix / budget + entered / k, threshold 0)
+                ls = capi.RerankLearnedStop()
+                budget = rp2.top_n
+                stages = [pfx for pfx in (16, 32, 48, 64, 96, 128, 192, 256, 384, 512) if pfx < budget]
+                ls.enabled, ls.num_stages, ls.top_k, ls.bootstrap_prefix = 1, len(stages), 10, 16
+                for i, pfx in enumerate(stages):
+                    ls.stage_prefixes[i] = pfx
+                while ls.initial_stage_index < ls.num_stages and ls.stage_prefixes[ls.initial_stage_index] <= 16:
+                    ls.initial_stage_index += 1
+                ls.linear_weights[1], ls.linear_weights[6], ls.bias, ls.threshold_logit = -2.5, 1.0, 1.0, 0.0
+                ls.inv_budget_top_n, ls.inv_top_k = 1.0 / budget, 0.1
+                if ls.initial_stage_index < ls.num_stages:
+                    res, ms = _time_calls(lambda: search.rerank_exact_learned_stop(ix, rp2, refined, q, model=ls,
+                                                                                   error_bounds=pq2["eps"]), args.reps)
+                    out["stages_ms"]["rerank_exact_learned_stop"] = ms
+                    print(f"rerank_exact_learned_stop {ms:.3f} ms  exact={res['n_exact']} filtered={res['n_filtered']} "
+                          f"mean_stop_prefix={float(res['stop_prefixes'].float().mean()):.1f} of {budget}")
+            if model is not None:
+                sr = search.Searcher(ix, Qn, cap, min(top_n, lr), args.entries)
+                sr.set_rvq(model, args.entries)
+                sr.set_pq2(search.Pq2Resources(codes=pq2["codes2"], tables_col_major=pq2["t2_cm"], centroid=pq2["c2"],
+                                               chunk_offsets=ix.pq_chunk_offsets, cross_terms=pq2["cross"],
+                                               error_bounds=pq2["eps"]), lr)
+                (oi, _, _), ms = _time_calls(lambda: sr.run_device(q, p, rp2), args.reps)
+                out["stages_ms"]["searcher_whole_path"] = ms
+                out["qps_whole_path"] = Qn / ms * 1e3
+                ids_k = _device_view(oi, Qn * 10, torch.int32).view(Qn, 10).cpu().numpy().view(np.uint32)
+                out["recall_at_10_whole_path"] = round(synth.recall_at_k(ids_k, gt, 10), 4)
+                print(f"searcher whole path (rvq, beam, table-free pq2 refine, bound-filtered rerank, top-k) {ms:.3f} ms "
+                      f"= {Qn / ms * 1e3:.0f} queries/s  recall@10={out['recall_at_10_whole_path']}")
+                sr.close()
+        return out
+
+    all_out = []
+    fractions = [float(x) for x in args.cached_fractions.split(",") if x] or [args.cached_fraction]
+    for frac in (fractions if adj_mapped is not None else [None]):
+        ix, label = base_ix, "adjacency + codes + vector pages in HBM"
+        if adj_mapped is not None or vec_mapped is not None:
+            kw = dict(num_nodes=base_ix.num_nodes, degree=base_ix.degree, dim=base_ix.dim, vector_kind=base_ix.vector_kind,
+                      codes=base_ix.codes, pq_tables_col_major=base_ix.pq_tables_col_major, pq_centroid=base_ix.pq_centroid,
+                      pq_chunk_offsets=base_ix.pq_chunk_offsets, vector_bytes=base_ix.vector_bytes,
+                      vectors_per_page=base_ix.vectors_per_page)
+            label = ""
+            if adj_mapped is not None:
+                cached = int(base_ix.num_nodes * frac)
+                kw.update(adjacency_bases=[adj_mapped], adjacency_cache=base_ix.adjacency[:cached] if cached else None,
+                          adjacency_cached_rows=cached)
+                label = f"adjacency in mapped pinned host memory, {cached} rows ({frac:.0%}) cached in HBM"
+                print(f"topology: {cached} rows ({frac:.0%}) cached in HBM")
+            else:
+                kw.update(adjacency=base_ix.adjacency)
+                label = "adjacency in HBM"
+            if vec_mapped is not None:
+                kw.update(vector_bases=[vec_mapped])
+                label += "; vector pages in mapped pinned host memory"
+            else:
+                kw.update(vector_pages=base_ix.vector_pages)
+                label += "; vector pages in HBM"
+            ix = search.DeviceIndex(**kw)
+        for top_l in top_ls:
+            all_out.append(time_case(ix, top_l, label))
     torch.cuda.synchronize()
     for hp in host_allocs:
         capi.check(lib.tann_host_free(hp))
-    print(json.dumps(out))
+    for o in all_out:
+        print(json.dumps(o))
 
 
 def _device_view(ptr, count, dtype):
@@ -555,9 +636,54 @@ def sharded_leg(args, rank, world, local, device):
             del full_ix, full_model
         del whole
     torch.cuda.empty_cache()
-    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms], dtype=torch.float64, device=device)
+    # ---- the same shards with the PQ codes replicated on every GPU (M bytes per node: 32 GB at one billion nodes,
+    # which 180 GB of HBM affords next to a 52 GB shard): code rows - most of the gather bytes - become local reads,
+    # adjacency rows and vector pages stay sharded ------------------------------------------------------------
+    rep_ms = rep_beam_ms = 0.0
+    rep_same = True
+    if s.total_nodes * M <= 40e9:
+        parts = [torch.empty_like(s.pq_codes) for _ in range(world)]
+        dist.all_gather(parts, s.pq_codes.contiguous())
+        all_codes = torch.cat(parts)
+        del parts
+        ix_r = dataclasses.replace(ix, codes=all_codes, codes_bases=None)
+        sr_r = search.Searcher(ix_r, Q, 1024, max_top_n, 128)
+        sr_r.set_rvq(model, 128)
+        ids_r, d_r, _ = sr_r.run_host(q_pinned.numpy(), tp, rp)
+        rep_same = bool(np.array_equal(ids_r, ids_sh) and np.array_equal(d_r.view(np.uint32), d_sh.view(np.uint32)))
+        for i in range(args.warmup):
+            sr_r.run_device(q_devs[i % nb], tp, rp)
+        barrier()
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record(stream)
+        for i in range(args.steps):
+            sr_r.run_device(q_devs[i % nb], tp, rp)
+        r1.record(stream)
+        barrier()
+        rep_ms = r0.elapsed_time(r1)
+        view_r = ix_r.view()
+
+        def beam_r():
+            capi.check(lib.tann_beam_search(C.byref(view_r), C.byref(bp), None, C.c_void_p(q_devs[0].data_ptr()),
+                                            capi.KIND_FLOAT32, Q, C.c_void_p(offs.data_ptr()), C.c_void_p(eids.data_ptr()),
+                                            C.c_void_p(cand.data_ptr()), C.c_void_p(stats_d.data_ptr()), None,
+                                            C.c_void_p(stream.cuda_stream)))
+        for _ in range(3):
+            beam_r()
+        barrier()
+        r0.record(stream)
+        for _ in range(args.steps):
+            beam_r()
+        r1.record(stream)
+        barrier()
+        rep_beam_ms = r0.elapsed_time(r1) / args.steps
+        sr_r.close()
+        del all_codes, ix_r
+        torch.cuda.empty_cache()
+    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms, rep_ms, rep_beam_ms, 0.0 if rep_same else 1.0], dtype=torch.float64,
+                         device=device)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, beam_ms = [float(x) for x in times.cpu()]
+    dev_ms, e2e_ms, beam_ms, rep_ms, rep_beam_ms, rep_bad = [float(x) for x in times.cpu()]
     sums = torch.tensor([beam_bytes, rerank_bytes], dtype=torch.float64, device=device)
     dist.all_reduce(sums)
     rec_t = torch.tensor([synth.recall_at_k(ids_sh, gt, 10) * (e - b), float(e - b)], dtype=torch.float64, device=device)
@@ -589,6 +715,11 @@ def sharded_leg(args, rank, world, local, device):
                         "remote_gbs_per_gpu": remote_gbs, "nvlink_frac": remote_gbs / NVLINK_INGRESS_GBS,
                         "nvlink_peak_gbs": NVLINK_INGRESS_GBS, "local_gbs_per_gpu": local_gbs,
                         "local_hbm_frac": local_gbs / hbm_peak},
+        "codes_replicated": (None if rep_ms == 0.0 else {
+            "what": f"the same shards with the PQ codes ({M} B per node) replicated on every GPU: code rows are read from local "
+                    "HBM, adjacency rows and vector pages stay sharded",
+            "value": total_q / (rep_ms * 1e-3), "unit": "queries/s", "ms_per_step": rep_ms / args.steps,
+            "beam_kernel_ms": round(rep_beam_ms, 4), "results_identical_to_sharded_codes": rep_bad == 0.0}),
         "ids_identical": ids_identical, "ids_checked_queries": checked,
         "ids_check": "sample of every rank's queries against the whole index searched unsharded on rank 0"
                      if ids_identical is not None else "skipped: the whole index does not fit one GPU beside the shards",

@@ -296,6 +296,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
     __shared__ float s_threshold, s_qnorm, s_prev_kth;
     __shared__ unsigned int s_exact, s_filtered, s_stable, s_stop;
     __shared__ float s_best[128];   // the top_k <= 128 smallest exact distances so far (bound filter, early stop)
+    __shared__ float s_tile[128], s_merged[128];   // a tile's distances, and the merged list under construction
     const bool track_kth = p.use_bound_filter || p.use_early_stop;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t dim = ix.dim;
@@ -379,10 +380,48 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
             ScoreRanks(ix, mode, keys, rank_ids, qrow, rb, rb + rc);
             __syncthreads();
             if (track_kth) {
-                if (tid == 0) {
-                    // k-th smallest exact distance over ranks [0, rb + rc) (:541-571): the sorted best-k
-                    // list is kept across tiles, only this tile's distances are inserted
-                    const uint32_t k = p.top_k;
+                // k-th smallest exact distance over ranks [0, rb + rc) (:541-571): the sorted best-k list is
+                // kept across tiles. A tile of up to 128 distances is merged in by counting: thread t places old
+                // entry t behind the tile's distances below it, and the tile's distance t behind the old entries
+                // not above it and the tile's distances in front of it (ties: the lower rank first). Only the
+                // values matter, so the order among equal values is free.
+                const uint32_t k = p.top_k;
+                if (rc <= (uint32_t)kRerankThreads) {
+                    const float inf = __int_as_float(0x7f800000);
+                    const float oldv = tid < k ? s_best[tid] : inf;
+                    const float newv = tid < rc ? FromOrderedBits((uint32_t)(keys[rb + tid] >> 32)) : inf;
+                    s_tile[tid] = newv;
+                    __syncthreads();
+                    uint32_t c_old = 0, c_new = 0;
+#pragma unroll 4
+                    for (uint32_t l = 0; l < rc; ++l) {
+                        const float x = s_tile[l];
+                        c_old += x < oldv ? 1u : 0u;
+                        c_new += (x < newv || (x == newv && l < tid)) ? 1u : 0u;
+                    }
+                    uint32_t lo = 0;   // old entries <= newv (fixed-trip binary search over the k sorted values)
+#pragma unroll
+                    for (uint32_t b = 128; b > 0; b >>= 1) {
+                        const uint32_t t = lo + b;
+                        if (t <= k && s_best[t - 1] <= newv) lo = t;
+                    }
+                    if (tid < k && tid + c_old < k) s_merged[tid + c_old] = oldv;
+                    if (tid < rc && lo + c_new < k) s_merged[lo + c_new] = newv;
+                    __syncthreads();
+                    if (tid < k) s_best[tid] = s_merged[tid];
+                    if (tid == 0) {
+                        const float kth = s_merged[k - 1];
+                        s_threshold = kth;
+                        if (p.use_early_stop) {   // src/io/bam_vector_provider.cu:1124-1135
+                            if (rb + rc >= p.early_stop_min_prefix && isfinite(kth)) {
+                                if (kth < s_prev_kth) s_stable = 0; else ++s_stable;
+                                if (s_stable >= p.early_stop_patience_tiles) s_stop = 1;
+                            }
+                            s_prev_kth = kth;
+                        }
+                    }
+                } else if (tid == 0) {
+                    // wider tiles: insertion by one thread
                     for (uint32_t r = rb; r < rb + rc; ++r) {
                         const float x = FromOrderedBits((uint32_t)(keys[r] >> 32));
                         if (!(x < s_best[k - 1])) continue;

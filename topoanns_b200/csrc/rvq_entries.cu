@@ -348,15 +348,15 @@ rvq_entries_tile_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
     }
 }
 
-// Codebook-in-shared-memory variant: one 512-thread block per SM keeps one level's transposed codebook
+// Codebook-in-shared-memory variant: one 576-thread block per SM keeps one level's transposed codebook
 // (count x dim floats, 128 KB at 256 x 128) in shared memory and scores all of its queries against it,
 // level 0 for every query first, then level 1 (the residual is recomputed from the query and the chosen
 // coarse centroid). All blocks of the other variants stream the same codebook rows from L2 at the same
 // moment, which serialises on the L2 slices that hold them; here a row crosses L2 once per SM and level.
-// Thread (qg, cg) owns queries 8 qg .. 8 qg + 7 of a 64-query tile and centroids 4 cg .. 4 cg + 3
+// Thread (qg, cg) owns queries 8 qg .. 8 qg + 7 of a 72-query tile and centroids 4 cg .. 4 cg + 3
 // (+ 256 per further pass); every dot product is the ascending-k FMA chain of the other variants.
-constexpr int kSmemThreads = 512;
-constexpr int kSmemTile = 64;          // queries per tile
+constexpr int kSmemThreads = 576;      // 9 query groups x 64 centroid groups
+constexpr int kSmemTile = 72;          // queries per tile: 10 000 queries over 148 SMs are one tile per block
 constexpr int kSmemMaxPerBlock = 1024; // queries per block
 
 __global__ void __launch_bounds__(kSmemThreads, 1)
@@ -410,9 +410,17 @@ rvq_entries_smem_kernel(const float* __restrict__ queries, uint64_t Q, uint32_t 
             const int nq = (int)min((uint32_t)QB, n_mine - t0);
             __syncthreads();   // cb is loaded; the previous tile's readers are done with x
             const uint32_t dim4 = dim / 4;
-#pragma unroll 4
-            for (uint32_t i = tid; i < (uint32_t)QB * dim4; i += kSmemThreads) {
-                const uint32_t qi = i / dim4, k = (i - qi * dim4) * 4;
+            // A warp takes 16 queries x 2 groups of four dims: its transposed stores then fall on 32 different
+            // banks (row stride XS = 76 words = 12 banks, 4 rows apart = 16 banks), and every query row is read
+            // in whole 32-byte sectors.
+            constexpr uint32_t kQ16 = (QB + 15) / 16;
+#pragma unroll 2
+            for (uint32_t i = tid; i < kQ16 * 16u * ((dim4 + 1u) & ~1u); i += kSmemThreads) {
+                const uint32_t l = i & 31u, wi = i >> 5;
+                const uint32_t qi = (wi % kQ16) * 16u + (l & 15u);
+                const uint32_t kg = (wi / kQ16) * 2u + (l >> 4);
+                if (qi >= (uint32_t)QB || kg >= dim4) continue;
+                const uint32_t k = kg * 4u;
                 float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if ((int)qi < nq) {
                     v = __ldg(reinterpret_cast<const float4*>(queries + (q_begin + t0 + qi) * dim + k));
@@ -572,8 +580,7 @@ cudaError_t LaunchRvqEntries(const float* queries, uint64_t Q, uint32_t dim, con
         const size_t max_count = nc > nf ? nc : nf;
         const size_t smem = (max_count + kSmemTile + 4) * (size_t)dim * 4;
         const uint64_t grid = (uint64_t)SmCount();
-        uint64_t per = (Q + grid - 1) / grid;
-        per = (per + 7) / 8 * 8;
+        const uint64_t per = (Q + grid - 1) / grid;   // an even share per SM; a share need not be a multiple of 8
         if (aligned && smem <= 200 * 1024 && per <= (uint64_t)kSmemMaxPerBlock) {
             cudaError_t e = cudaFuncSetAttribute(rvq_entries_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return e;

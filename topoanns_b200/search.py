@@ -543,6 +543,17 @@ def device_index_from_arrays(*, adjacency, codes, vectors, pq_tables_row_major, 
 
 
 def device_index_from_synth(s, device="cuda") -> DeviceIndex:
+    if isinstance(s.vectors, torch.Tensor) and s.vectors.is_cuda and torch.device(device).type == "cuda":
+        # everything already lives on the device: lay the vector pages out there, no trip through host memory
+        from . import sharding
+        vb = s.vectors.shape[1] * s.vectors.element_size()
+        adj = s.adjacency if s.adjacency.dtype == torch.int32 else s.adjacency.to(torch.int32)
+        return DeviceIndex(
+            num_nodes=adj.shape[0], degree=adj.shape[1], dim=s.vectors.shape[1], vector_kind=kind_of(s.vectors),
+            adjacency=adj.contiguous(), codes=s.pq_codes.contiguous(), vector_pages=sharding.pages_from_rows(s.vectors),
+            pq_tables_col_major=s.pq_tables.float().t().contiguous(), pq_centroid=s.pq_centroid.float().contiguous(),
+            pq_chunk_offsets=s.pq_chunk_offsets.to(torch.int32).contiguous(), vector_bytes=vb,
+            vectors_per_page=4096 // vb, page_bytes=4096)
     return device_index_from_arrays(adjacency=s.adjacency, codes=s.pq_codes, vectors=s.vectors,
                                     pq_tables_row_major=s.pq_tables, pq_centroid=s.pq_centroid,
                                     pq_chunk_offsets=s.pq_chunk_offsets, device=device)

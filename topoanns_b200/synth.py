@@ -60,7 +60,9 @@ CONFIGS = {
                         rvq=True),
     "cfg4": SynthConfig("cfg4", 1_000_000_000, 128, "uint8", 100_000, knn_edges=24, random_edges=8,
                         pq_chunks=32, num_queries=10_000, rvq=True),
-    "cfg5": SynthConfig("cfg5", 10_000_000, 768, "float32", 10_000, knn_edges=48, random_edges=16,
+    # sigma scales the rank-64 part: 0.05 per latent dim keeps a component's spread (~0.4) below the distance
+    # between unit-norm centres (~1.4), so that components stay separate after normalisation
+    "cfg5": SynthConfig("cfg5", 10_000_000, 768, "float32", 10_000, sigma=0.05, knn_edges=48, random_edges=16,
                         pq_chunks=96, num_queries=10_000, normalise=True, low_rank=64, rvq=True),
 }
 
@@ -242,14 +244,32 @@ def build(cfg: SynthConfig, device="cpu") -> SynthIndex:
         comp_ids = torch.arange(s, e, device=dev) // n_per
         grouped[s:e] = _sample_component(cfg, centres, comp_ids, gen, basis).to(out_dtype)
     # graph in grouped order, then shuffle ids
-    knn = build_knn_graph(grouped, n_per, cfg.knn_edges)
-    perm = torch.randperm(N, generator=gen, device=dev)          # new id of grouped row i
-    rand_edges = torch.randint(0, N, (N, cfg.random_edges), generator=gen, device=dev)
-    adjacency = torch.empty((N, knn.shape[1] + cfg.random_edges), dtype=torch.int32, device=dev)
-    adjacency[perm] = torch.cat([perm[knn], rand_edges], 1).to(torch.int32)
-    del knn, rand_edges
+    if N <= (1 << 25):
+        knn = build_knn_graph(grouped, n_per, cfg.knn_edges)
+        perm = torch.randperm(N, generator=gen, device=dev)          # new id of grouped row i
+        rand_edges = torch.randint(0, N, (N, cfg.random_edges), generator=gen, device=dev)
+        adjacency = torch.empty((N, knn.shape[1] + cfg.random_edges), dtype=torch.int32, device=dev)
+        adjacency[perm] = torch.cat([perm[knn], rand_edges], 1).to(torch.int32)
+        del knn, rand_edges
+    else:
+        # very large indices: the same construction in slices of whole components, so that the 64-bit
+        # neighbour tables of a slice (not of the whole index) exist at any time
+        perm = torch.randperm(N, generator=gen, device=dev)
+        kk = min(cfg.knn_edges, n_per - 1)
+        adjacency = torch.empty((N, kk + cfg.random_edges), dtype=torch.int32, device=dev)
+        slice_rows = max(1, (1 << 22) // n_per) * n_per
+        for b in range(0, N, slice_rows):
+            e = min(N, b + slice_rows)
+            knn = build_knn_graph(grouped[b:e], n_per, cfg.knn_edges) + b
+            rnd = torch.randint(0, N, (e - b, cfg.random_edges), generator=gen, device=dev)
+            adjacency[perm[b:e]] = torch.cat([perm[knn], rnd], 1).to(torch.int32)
+            del knn, rnd
     vectors = torch.empty_like(grouped)
-    vectors[perm] = grouped
+    if N <= (1 << 25):
+        vectors[perm] = grouped
+    else:
+        for b in range(0, N, 1 << 24):
+            vectors[perm[b:b + (1 << 24)]] = grouped[b:b + (1 << 24)]
     component_of = torch.empty(N, dtype=torch.int32, device=dev)
     component_of[perm] = (torch.arange(N, device=dev) // n_per).to(torch.int32)
     del grouped
