@@ -164,3 +164,32 @@ def test_pq_and_aux_files(tmp_path):
     formats.write_gt(tmp_path / "gt.bin", np.arange(10, dtype=np.int32).reshape(5, 2), np.ones((5, 2), np.float32))
     gi, gd = formats.read_gt(tmp_path / "gt.bin")
     assert gi.shape == (5, 2) and gd.shape == (5, 2)
+
+
+def test_hpq_selector_file_and_learned_stop_model_file(tmp_path):
+    # selector bits: int32 rows, int32 cols, rows x cols bytes (src/io/hpq_index.cpp:69-86); shape checks as the loader's
+    rng = np.random.default_rng(3)
+    bits = rng.integers(0, 256, size=(37, 6), dtype=np.uint8)
+    formats.write_hpq_selector_bits(tmp_path / "sel.bin", bits)
+    raw = (tmp_path / "sel.bin").read_bytes()
+    assert struct.unpack_from("<ii", raw, 0) == (37, 6) and len(raw) == 8 + 37 * 6
+    assert np.array_equal(formats.read_hpq_selector_bits(tmp_path / "sel.bin", 37, 48), bits)
+    with pytest.raises(ValueError, match="shape does not match"):
+        formats.read_hpq_selector_bits(tmp_path / "sel.bin", 37, 64)
+    # learned traversal-stop model file folded for one top_l (src/search/topology_search_kernel.cu:248-380)
+    from topoanns_b200 import search
+    path = tmp_path / "stop.txt"
+    path.write_text("# comment\nstage_prefixes = 0, 8,16, 64,200\nfeature_means = " + ",".join(["0.5"] * 12) + "\n"
+                    "feature_inv_stds = " + ",".join(["2.0"] * 12) + "\nweights = " + ",".join(str(i) for i in range(12)) + "\n"
+                    "bias = 1.0\nthreshold_logit = 0.25\nthreshold_logit_top_l_64 = -0.5\ntopk_churn_mode = flag\n"
+                    "feature_mask = 1,1,0,1\n")
+    ls = search.load_learned_stop(path, 64, 10)
+    assert ls.enabled == 1 and ls.top_k == 10 and ls.topk_churn_flag_mode == 1 and ls.next64_flag_mode == 0
+    assert [ls.stage_prefixes[i] for i in range(ls.num_stages)] == [8, 16]          # 0, 64 >= top_l and 200 are dropped
+    assert ls.threshold_logit == -0.5 and abs(ls.inv_top_l - 1.0 / 64) < 1e-9
+    assert ls.weights[1] == 2.0 and ls.weights[2] == 0.0 and ls.weights[5] == 10.0  # weight / std, masked feature -> 0
+    assert abs(ls.bias - (1.0 - 0.5 * sum(2.0 * i for i in range(12) if i != 2))) < 1e-4
+    assert search.load_learned_stop(path, 128, 10).threshold_logit == 0.25
+    path.write_text("weights = 1,2\nfeature_means = 1\nfeature_inv_stds = 1\n")
+    with pytest.raises(ValueError, match="length 12"):
+        search.load_learned_stop(path, 64, 10)
