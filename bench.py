@@ -45,7 +45,8 @@ METRIC = "QPS at recall@10>=0.95 (10M uint8 d=128, 1 batch of 10k queries per GP
 L_SWEEP = (16, 32, 64, 128, 256, 512, 1024)
 TOPN_SWEEP = (32, 128, 192, 256, 512)
 DEFAULT_POINT = (16, 192)   # (top_l, rerank_top_n): fastest sweep point with recall@10 >= 0.95 on the seeded cfg2 data
-SHARDED_POINTS = ((16, 256), (32, 256), (32, 512), (64, 512))   # candidates for the degree-32 sharded index
+# candidates for the degree-32 sharded index (its recall falls as the index grows with the number of GPUs)
+SHARDED_POINTS = ((16, 256), (32, 256), (32, 512), (64, 512), (64, 1024), (128, 1024))
 # DRAM traffic of one beam_search_kernel launch (10 k queries, 10 M nodes), ncu dram__bytes_read.sum +
 # dram__bytes_write.sum, keyed by (top_l, candidate capacity) - the kernel does not depend on rerank_top_n
 # beyond the capacity it implies; summarised under profiles/.

@@ -266,11 +266,25 @@ __device__ void SortKeysShared(unsigned long long* keys, uint32_t F) {
     }
 }
 
+// Row n of an array: the plain form knows there is one shard.
+template <bool kOneShard>
+__device__ __forceinline__ const uint8_t* Row(const TannShards& s, uint64_t n, uint64_t row_bytes) {
+    if constexpr (kOneShard) return static_cast<const uint8_t*>(s.base[0]) + n * row_bytes;
+    else return ShardRow(s, n, row_bytes);
+}
+
 // kSingle: W * degree <= 128, so every thread owns at most one frontier slot per batch: its key
 // stays in a register until the survivors are compacted and rank-sorted.
-template <int kM, bool kSingle>
+// kSub > 0 selects the plain form: no caller-provided table, no learned stop, the default stop prefix, at most 128 list
+// ranks that matter (top_l <= 128), every array in one shard and no adjacency cache - the launcher checks these - with
+// chunks kSub dims wide (checked here; other widths take the generic table builder). Compiling those paths out shrinks
+// the loop that five blocks in different phases run at once.
+// The plain form is also compiled per layout (kNbr: 1 = neighbour-code layout present, 0 = absent, -1 = look at the
+// index view) and for lists whose traversal prefix fits one bitmap word (kOneWord: top_l <= 32).
+template <int kM, bool kSingle, int kSub, int kNbr = -1, bool kOneWord = false>
 __global__ void __launch_bounds__(kBeamThreads)
 beam_search_kernel(const __grid_constant__ BeamArgs a) {
+    constexpr bool kPlain = kSub > 0;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t M = kM > 0 ? (uint32_t)kM : a.ix.num_chunks;
     const uint32_t C = a.p.candidate_capacity;
@@ -304,13 +318,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 
     __shared__ __align__(8) unsigned long long lut_barrier;   // completion of the bulk copy of a caller's table
     uint32_t lut_phase = 0;
-    if (a.lut != nullptr) {
+    if (!kPlain && a.lut != nullptr) {
         if (tid == 0) BarrierInit(&lut_barrier, 1);
         __syncthreads();
     }
     // Chunks of equal width (the usual case) take the unrolled table build.
     uint32_t uniform_sub = 0;
-    if (a.lut == nullptr) {
+    if (kPlain || a.lut == nullptr) {
         const uint32_t sub0 = __ldg(a.ix.pq_chunk_offsets + 1) - __ldg(a.ix.pq_chunk_offsets);
         bool same = __ldg(a.ix.pq_chunk_offsets) == 0u;
         for (uint32_t i = tid; i < M; i += kBeamThreads)
@@ -325,7 +339,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
 #endif
         // ---- per-query set-up --------------------------------------------------------------
         bool lut_copy_pending = false;
-        if (a.lut != nullptr) {
+        if (!kPlain && a.lut != nullptr) {
             // A table given by the caller is staged with one bulk asynchronous copy while the block clears
             // its lists.
             const float* src_lut = a.lut + q * (uint64_t)M * kCentroids;
@@ -338,6 +352,10 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 sq[i] = LoadAsFloat<float>(a.queries, a.query_kind, q * d + i) - __ldg(a.ix.pq_centroid + i);
             for (uint32_t i = tid; i <= M; i += kBeamThreads) offs[i] = __ldg(a.ix.pq_chunk_offsets + i);
             __syncthreads();
+            if constexpr (kPlain) {
+                if (uniform_sub == (uint32_t)kSub) BuildLutUniform<kSub, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid);
+                else BuildLutGeneric<kBeamThreads>(lut, sq, offs, a.ix.pq_tables_col_major, M, tid);
+            } else
             switch (uniform_sub) {
                 case 1: BuildLutUniform<1, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
                 case 2: BuildLutUniform<2, kBeamThreads>(lut, sq, a.ix.pq_tables_col_major, M, tid); break;
@@ -404,20 +422,20 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 uint32_t stop = 0, nsel = 0;
                 if (expanded >= a.p.max_expansions || valid == 0) {
                     stop = 2;
-                } else if (a.p.learned_stop.enabled) {
+                } else if (!kPlain && a.p.learned_stop.enabled) {
                     if (tid == 0)
                         ctl.stop = LearnedStop(a.p.learned_stop, ctl, valid, visited, expanded, cur, unexp, L) ? 2u : 0u;
                     __syncthreads();
                     stop = ctl.stop;
                 }
                 if (!stop) {
-                    const bool prefix_stop = a.p.stop_prefix != 0 && a.p.stop_prefix < L;
-                    if (UW <= 4) {
+                    const bool prefix_stop = !kPlain && a.p.stop_prefix != 0 && a.p.stop_prefix < L;
+                    if (kPlain || UW <= 4) {
                         // up to 128 list ranks: every thread reads the whole bitmap and finds the
                         // pick of its own slot directly (no scan, no exchange)
                         uint32_t wd[4];
 #pragma unroll
-                        for (uint32_t u = 0; u < 4; ++u) wd[u] = u < UW ? unexp[u] : 0u;
+                        for (uint32_t u = 0; u < 4; ++u) wd[u] = (u < UW && (!kOneWord || u == 0)) ? unexp[u] : 0u;
                         bool any;
                         if (prefix_stop && a.p.stop_use_expanded) {
                             any = !(valid >= L && expanded >= a.p.stop_prefix);
@@ -547,16 +565,16 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                         if (kSingle) { k = my_k; j = my_j; } else { k = s / deg; j = s - k * deg; }
                         if (kSingle && UW <= 4) node = my_node; else node = s_sel[tid >> 5][k];
                         const uint32_t* row =
-                            (node < a.ix.adjacency_cached_rows)
+                            (!kPlain && node < a.ix.adjacency_cached_rows)
                                 ? a.ix.adjacency_cache + (uint64_t)node * deg
                                 : reinterpret_cast<const uint32_t*>(
-                                      ShardRow(a.ix.adjacency, node, (uint64_t)deg * 4));
+                                      Row<kPlain>(a.ix.adjacency, node, (uint64_t)deg * 4));
                         id = __ldg(row + j);
                         // With the neighbour-code layout the slot's code row sits at (node, j): its address
                         // does not depend on the id just requested, so both loads share one round trip.
                         if constexpr (kSingle && kM > 0) {
-                            if (a.ix.neighbor_codes.base[0] != nullptr) {
-                                LoadCodeWords<kM>(ShardRow(a.ix.neighbor_codes, node, (uint64_t)deg * kM) + (size_t)j * kM, my_words);
+                            if (kNbr < 0 ? a.ix.neighbor_codes.base[0] != nullptr : kNbr == 1) {
+                                LoadCodeWords<kM>(Row<kPlain>(a.ix.neighbor_codes, node, (uint64_t)deg * kM) + (size_t)j * kM, my_words);
                                 codes_requested = true;
                             }
                         }
@@ -573,7 +591,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (kSingle) my_bits = bits;
                 // The code row does not depend on the barrier below: request it now.
                 if constexpr (kSingle && kM > 0)
-                    if (pass && !codes_requested) LoadCodeWords<kM>(ShardRow(a.ix.codes, id, M), my_words);
+                    if (pass && !codes_requested) LoadCodeWords<kM>(Row<kPlain>(a.ix.codes, id, M), my_words);
                 // Park the surviving id in the key slot; phase 2 turns it into a key.
                 const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
                 if (kSingle) {
@@ -606,7 +624,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     if constexpr (kSingle && kM > 0) {
                         dist = AdcFromWords<kM>(lut, my_words);
                     } else {
-                        dist = AdcTreeThread<kM>(lut, ShardRow(a.ix.codes, id, M), M);
+                        dist = AdcTreeThread<kM>(lut, Row<kPlain>(a.ix.codes, id, M), M);
                     }
                     const unsigned long long key = ((unsigned long long)OrderedBits(dist) << 32) | id;
                     if (kSingle) my_key = key; else fkey[s] = key;
@@ -715,7 +733,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                             }
                         }
                         nxt[rank + lo] = k;
-                        if (rank + lo < a.p.learned_stop.top_k) ctl.ls_topk_changed = 1;
+                        if (!kPlain && rank + lo < a.p.learned_stop.top_k) ctl.ls_topk_changed = 1;
                     }
                 }
                 accepted = __syncthreads_count(pred);
@@ -854,21 +872,49 @@ typedef void (*BeamKernel)(const BeamArgs);
 template <bool kSingle>
 static BeamKernel PickByChunks(uint32_t M) {
     switch (M) {
-        case 16: return beam_search_kernel<16, kSingle>;
-        case 32: return beam_search_kernel<32, kSingle>;
-        case 48: return beam_search_kernel<48, kSingle>;
-        case 64: return beam_search_kernel<64, kSingle>;
-        case 96: return beam_search_kernel<96, kSingle>;
-        default: return beam_search_kernel<0, kSingle>;
+        case 16: return beam_search_kernel<16, kSingle, 0>;
+        case 32: return beam_search_kernel<32, kSingle, 0>;
+        case 48: return beam_search_kernel<48, kSingle, 0>;
+        case 64: return beam_search_kernel<64, kSingle, 0>;
+        case 96: return beam_search_kernel<96, kSingle, 0>;
+        default: return beam_search_kernel<0, kSingle, 0>;
     }
 }
 
-BeamKernel PickBeamKernel(uint32_t M, uint32_t slots) {
+// The plain form exists for the chunk counts and widths of the benchmark configurations (128 dims in 32 chunks,
+// 96 in 48, 768 in 96) with at most 128 slots per batch.
+static bool PlainCase(const BeamArgs& a) {
+    const TannIndexView& ix = a.ix;
+    const TannBeamParams& p = a.p;
+    return a.lut == nullptr && !p.learned_stop.enabled && (p.stop_prefix == 0 || p.stop_prefix >= p.top_l) &&
+           !p.stop_use_expanded && p.top_l <= 128 && ix.adjacency.num_shards <= 1 && ix.codes.num_shards <= 1 &&
+           ix.neighbor_codes.num_shards <= 1 && ix.adjacency_cached_rows == 0 &&
+           p.search_width * ix.degree <= (uint32_t)kBeamThreads;
+}
+
+template <int kM, int kSub>
+static BeamKernel PickPlain(bool nbr, bool one_word) {
+    if (nbr) return one_word ? beam_search_kernel<kM, true, kSub, 1, true> : beam_search_kernel<kM, true, kSub, 1, false>;
+    return one_word ? beam_search_kernel<kM, true, kSub, 0, true> : beam_search_kernel<kM, true, kSub, 0, false>;
+}
+
+BeamKernel PickBeamKernel(uint32_t M, uint32_t slots, uint32_t plain_sub, bool nbr, bool one_word) {
+    if (plain_sub != 0 && slots <= (uint32_t)kBeamThreads) {
+        if (M == 32 && plain_sub == 4) return PickPlain<32, 4>(nbr, one_word);
+        if (M == 48 && plain_sub == 2) return PickPlain<48, 2>(nbr, one_word);
+        if (M == 96 && plain_sub == 8) return PickPlain<96, 8>(nbr, one_word);
+    }
     return slots <= (uint32_t)kBeamThreads ? PickByChunks<true>(M) : PickByChunks<false>(M);
 }
 
+static uint32_t PlainSub(const BeamArgs& a) {
+    if (!PlainCase(a) || a.ix.num_chunks == 0 || a.ix.dim % a.ix.num_chunks != 0) return 0;
+    return a.ix.dim / a.ix.num_chunks;
+}
+
 cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream_t stream) {
-    BeamKernel k = PickBeamKernel(a.ix.num_chunks, a.p.search_width * a.ix.degree);
+    BeamKernel k = PickBeamKernel(a.ix.num_chunks, a.p.search_width * a.ix.degree, PlainSub(a),
+                                  a.ix.neighbor_codes.base[0] != nullptr, a.p.top_l <= 32);
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     k<<<grid, kBeamThreads, smem, stream>>>(a);
@@ -876,7 +922,7 @@ cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream
 }
 
 cudaError_t BeamOccupancy(uint32_t M, uint32_t slots, size_t smem, int* blocks_per_sm) {
-    BeamKernel k = PickBeamKernel(M, slots);
+    BeamKernel k = PickBeamKernel(M, slots, 0, false, false);   // the plain forms use the same shared memory and no more registers
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, k, kBeamThreads, smem);
