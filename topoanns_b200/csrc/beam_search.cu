@@ -276,15 +276,16 @@ __device__ __forceinline__ const uint8_t* Row(const TannShards& s, uint64_t n, u
 // kSingle: W * degree <= 128, so every thread owns at most one frontier slot per batch: its key
 // stays in a register until the survivors are compacted and rank-sorted.
 // kSub > 0 selects the plain form: no caller-provided table, no learned stop, the default stop prefix, at most 128 list
-// ranks that matter (top_l <= 128), every array in one shard and no adjacency cache - the launcher checks these - with
+// ranks that matter (top_l <= 128), no adjacency cache and (unless kSharded) every array in one shard - the launcher checks these - with
 // chunks kSub dims wide (checked here; other widths take the generic table builder). Compiling those paths out shrinks
 // the loop that five blocks in different phases run at once.
 // The plain form is also compiled per layout (kNbr: 1 = neighbour-code layout present, 0 = absent, -1 = look at the
 // index view) and for lists whose traversal prefix fits one bitmap word (kOneWord: top_l <= 32).
-template <int kM, bool kSingle, int kSub, int kNbr = -1, bool kOneWord = false>
+template <int kM, bool kSingle, int kSub, int kNbr = -1, bool kOneWord = false, bool kSharded = false>
 __global__ void __launch_bounds__(kBeamThreads)
 beam_search_kernel(const __grid_constant__ BeamArgs a) {
     constexpr bool kPlain = kSub > 0;
+    constexpr bool kOneShard = kPlain && !kSharded;   // rows of node-id-range shards are resolved per gather
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const uint32_t M = kM > 0 ? (uint32_t)kM : a.ix.num_chunks;
     const uint32_t C = a.p.candidate_capacity;
@@ -568,13 +569,13 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                             (!kPlain && node < a.ix.adjacency_cached_rows)
                                 ? a.ix.adjacency_cache + (uint64_t)node * deg
                                 : reinterpret_cast<const uint32_t*>(
-                                      Row<kPlain>(a.ix.adjacency, node, (uint64_t)deg * 4));
+                                      Row<kOneShard>(a.ix.adjacency, node, (uint64_t)deg * 4));
                         id = __ldg(row + j);
                         // With the neighbour-code layout the slot's code row sits at (node, j): its address
                         // does not depend on the id just requested, so both loads share one round trip.
                         if constexpr (kSingle && kM > 0) {
                             if (kNbr < 0 ? a.ix.neighbor_codes.base[0] != nullptr : kNbr == 1) {
-                                LoadCodeWords<kM>(Row<kPlain>(a.ix.neighbor_codes, node, (uint64_t)deg * kM) + (size_t)j * kM, my_words);
+                                LoadCodeWords<kM>(Row<kOneShard>(a.ix.neighbor_codes, node, (uint64_t)deg * kM) + (size_t)j * kM, my_words);
                                 codes_requested = true;
                             }
                         }
@@ -591,7 +592,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 if (kSingle) my_bits = bits;
                 // The code row does not depend on the barrier below: request it now.
                 if constexpr (kSingle && kM > 0)
-                    if (pass && !codes_requested) LoadCodeWords<kM>(Row<kPlain>(a.ix.codes, id, M), my_words);
+                    if (pass && !codes_requested) LoadCodeWords<kM>(Row<kOneShard>(a.ix.codes, id, M), my_words);
                 // Park the surviving id in the key slot; phase 2 turns it into a key.
                 const unsigned long long parked = pass ? (unsigned long long)id : kInvalidKey;
                 if (kSingle) {
@@ -624,7 +625,7 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     if constexpr (kSingle && kM > 0) {
                         dist = AdcFromWords<kM>(lut, my_words);
                     } else {
-                        dist = AdcTreeThread<kM>(lut, Row<kPlain>(a.ix.codes, id, M), M);
+                        dist = AdcTreeThread<kM>(lut, Row<kOneShard>(a.ix.codes, id, M), M);
                     }
                     const unsigned long long key = ((unsigned long long)OrderedBits(dist) << 32) | id;
                     if (kSingle) my_key = key; else fkey[s] = key;
@@ -887,22 +888,23 @@ static bool PlainCase(const BeamArgs& a) {
     const TannIndexView& ix = a.ix;
     const TannBeamParams& p = a.p;
     return a.lut == nullptr && !p.learned_stop.enabled && (p.stop_prefix == 0 || p.stop_prefix >= p.top_l) &&
-           !p.stop_use_expanded && p.top_l <= 128 && ix.adjacency.num_shards <= 1 && ix.codes.num_shards <= 1 &&
-           ix.neighbor_codes.num_shards <= 1 && ix.adjacency_cached_rows == 0 &&
+           !p.stop_use_expanded && p.top_l <= 128 && ix.adjacency_cached_rows == 0 &&
            p.search_width * ix.degree <= (uint32_t)kBeamThreads;
 }
 
 template <int kM, int kSub>
-static BeamKernel PickPlain(bool nbr, bool one_word) {
+static BeamKernel PickPlain(bool nbr, bool one_word, bool sharded) {
+    if (sharded)   // node-id-range shards: the layout is looked up in the index view
+        return one_word ? beam_search_kernel<kM, true, kSub, -1, true, true> : beam_search_kernel<kM, true, kSub, -1, false, true>;
     if (nbr) return one_word ? beam_search_kernel<kM, true, kSub, 1, true> : beam_search_kernel<kM, true, kSub, 1, false>;
     return one_word ? beam_search_kernel<kM, true, kSub, 0, true> : beam_search_kernel<kM, true, kSub, 0, false>;
 }
 
-BeamKernel PickBeamKernel(uint32_t M, uint32_t slots, uint32_t plain_sub, bool nbr, bool one_word) {
+BeamKernel PickBeamKernel(uint32_t M, uint32_t slots, uint32_t plain_sub, bool nbr, bool one_word, bool sharded) {
     if (plain_sub != 0 && slots <= (uint32_t)kBeamThreads) {
-        if (M == 32 && plain_sub == 4) return PickPlain<32, 4>(nbr, one_word);
-        if (M == 48 && plain_sub == 2) return PickPlain<48, 2>(nbr, one_word);
-        if (M == 96 && plain_sub == 8) return PickPlain<96, 8>(nbr, one_word);
+        if (M == 32 && plain_sub == 4) return PickPlain<32, 4>(nbr, one_word, sharded);
+        if (M == 48 && plain_sub == 2) return PickPlain<48, 2>(nbr, one_word, sharded);
+        if (M == 96 && plain_sub == 8) return PickPlain<96, 8>(nbr, one_word, sharded);
     }
     return slots <= (uint32_t)kBeamThreads ? PickByChunks<true>(M) : PickByChunks<false>(M);
 }
@@ -914,7 +916,8 @@ static uint32_t PlainSub(const BeamArgs& a) {
 
 cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream_t stream) {
     BeamKernel k = PickBeamKernel(a.ix.num_chunks, a.p.search_width * a.ix.degree, PlainSub(a),
-                                  a.ix.neighbor_codes.base[0] != nullptr, a.p.top_l <= 32);
+                                  a.ix.neighbor_codes.base[0] != nullptr, a.p.top_l <= 32,
+                                  a.ix.adjacency.num_shards > 1 || a.ix.codes.num_shards > 1 || a.ix.neighbor_codes.num_shards > 1);
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     k<<<grid, kBeamThreads, smem, stream>>>(a);
@@ -922,7 +925,7 @@ cudaError_t LaunchBeam(const BeamArgs& a, size_t smem, uint32_t grid, cudaStream
 }
 
 cudaError_t BeamOccupancy(uint32_t M, uint32_t slots, size_t smem, int* blocks_per_sm) {
-    BeamKernel k = PickBeamKernel(M, slots, 0, false, false);   // the plain forms use the same shared memory and no more registers
+    BeamKernel k = PickBeamKernel(M, slots, 0, false, false, false);   // the plain forms use the same shared memory and no more registers
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     return cudaOccupancyMaxActiveBlocksPerMultiprocessor(blocks_per_sm, k, kBeamThreads, smem);
