@@ -46,7 +46,7 @@ L_SWEEP = (16, 32, 64, 128, 256, 512, 1024)
 TOPN_SWEEP = (32, 128, 192, 256, 512)
 DEFAULT_POINT = (16, 192)   # (top_l, rerank_top_n): fastest sweep point with recall@10 >= 0.95 on the seeded cfg2 data
 # candidates for the degree-32 sharded index (its recall falls as the index grows with the number of GPUs)
-SHARDED_POINTS = ((16, 256), (32, 256), (32, 512), (64, 512), (64, 1024), (128, 1024))
+SHARDED_POINTS = ((16, 256), (32, 256), (32, 512), (64, 512), (64, 1024), (128, 1024), (128, 2048))
 # DRAM traffic of one beam_search_kernel launch (10 k queries, 10 M nodes), ncu dram__bytes_read.sum +
 # dram__bytes_write.sum, keyed by (top_l, candidate capacity) - the kernel does not depend on rerank_top_n
 # beyond the capacity it implies; summarised under profiles/.
@@ -79,6 +79,10 @@ def parse_args():
     ap.add_argument("--shard-nodes", type=int, default=10_000_000,
                     help="N > 1: rows per GPU of the node-id-range-sharded leg (R = 32 records as in the 1 B-vector configuration)")
     ap.add_argument("--no-sharded-leg", action="store_true", help="N > 1: skip the node-id-range-sharded leg")
+    ap.add_argument("--shard-gt-stride", type=int, default=1,
+                    help="N > 1: brute-force ground truth of the sharded leg for every n-th query only (very large shards)")
+    ap.add_argument("--sharded-only", action="store_true",
+                    help="N > 1: run only the sharded leg and print its record as the line (very large shards)")
     ap.add_argument("--stages", action="store_true",
                     help="per-stage CUDA-event timings of one synthetic case (1 GPU), one line per stage; for profilers")
     ap.add_argument("--top-l-values", default="", help="--stages: comma-separated top_l values timed on one index build")
@@ -502,20 +506,29 @@ def sharded_leg(args, rank, world, local, device):
     lib = capi.load()
     Q = args.queries
     t0 = time.time()
-    cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=args.shard_nodes * world, num_queries=Q * world,
-                              components=max(world, args.shard_nodes * world // 1000), kmeans_iters=5, train_sample=65536)
-    s = synth_sharded.build(cfg, device)       # this rank's shard + the whole query set and ground truth
+    # Mixture components of 1000 nodes whatever the size of the index: larger components of this isotropic mixture
+    # cannot be ranked by 32-byte PQ codes (4000-node components gave recall@10 0.58 with 2048 candidates reranked).
+    total = args.shard_nodes * world
+    cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=total, num_queries=Q * world,
+                              components=max(world, total // 1000), kmeans_iters=5, train_sample=65536)
+    s = synth_sharded.build(cfg, device, gt_stride=max(1, args.shard_gt_stride))   # this rank's shard + all queries + ground truth
     torch.cuda.synchronize()
     build_s = time.time() - t0
     b, e = sharding.query_shard(s.queries.shape[0], world, rank)
-    gt = s.gt_ids.cpu().numpy()[b:e]
+    gt_all = s.gt_ids.cpu().numpy()[b:e]
+    has_gt = gt_all[:, 0] >= 0            # with a ground-truth stride only these rows count for recall
+    gt = gt_all[has_gt]
     my_queries = s.queries[b:e].contiguous()
     degree, M = s.adjacency.shape[1], s.pq_codes.shape[1]
     ix, peer_buffers = sharding.peer_index_from_sharded(s)
+    whole_bytes = s.total_nodes * (degree * 4 + M + ix.vector_bytes)
+    if whole_bytes > 60e9:     # no unsharded self-check at this size: the generator's copies of the shard can go
+        s.vectors, s.adjacency = s.vectors[:0], s.adjacency[:0]
+        torch.cuda.empty_cache()
     model = search.RvqModel(dim=s.cfg.dim, coarse=s.rvq_coarse.contiguous(), fine=s.rvq_fine.contiguous(),
                             bucket_sizes=s.rvq_buckets[0], cluster_offsets=s.rvq_buckets[1], cluster_ids=s.rvq_buckets[2])
     max_top_n = max(tn for _, tn in SHARDED_POINTS)
-    sr = search.Searcher(ix, Q, 1024, max_top_n, 128)
+    sr = search.Searcher(ix, Q, max_top_n, max_top_n, 128)
     sr.set_rvq(model, 128)
     q_pinned = my_queries.cpu().pin_memory()
     # operating point: the fastest candidate whose recall@10 over ALL ranks' queries reaches the target
@@ -528,7 +541,8 @@ def sharded_leg(args, rank, world, local, device):
         t1 = time.perf_counter()
         ids, _, _ = sr.run_host(q_pinned.numpy(), tp, rp)
         dt = time.perf_counter() - t1
-        agg = torch.tensor([synth.recall_at_k(ids, gt, 10) * (e - b), float(e - b), 0.0], dtype=torch.float64, device=device)
+        n_gt = int(has_gt.sum())
+        agg = torch.tensor([synth.recall_at_k(ids[has_gt], gt, 10) * n_gt, float(n_gt), 0.0], dtype=torch.float64, device=device)
         dist.all_reduce(agg)
         worst = torch.tensor([dt], dtype=torch.float64, device=device)
         dist.all_reduce(worst, op=dist.ReduceOp.MAX)
@@ -619,7 +633,6 @@ def sharded_leg(args, rank, world, local, device):
     all_ids, all_d = sharding.gather_topk(torch.from_numpy(ids_sh.view(np.int32)).to(device),
                                           torch.from_numpy(d_sh).to(device), Q * world)
     ids_identical, checked = None, 0
-    whole_bytes = s.total_nodes * (degree * 4 + M + ix.vector_bytes)
     if whole_bytes <= 60e9:
         whole = synth_sharded.gather_whole(s)
         if rank == 0:
@@ -648,7 +661,7 @@ def sharded_leg(args, rank, world, local, device):
         all_codes = torch.cat(parts)
         del parts
         ix_r = dataclasses.replace(ix, codes=all_codes, codes_bases=None)
-        sr_r = search.Searcher(ix_r, Q, 1024, max_top_n, 128)
+        sr_r = search.Searcher(ix_r, Q, max_top_n, max_top_n, 128)
         sr_r.set_rvq(model, 128)
         ids_r, d_r, _ = sr_r.run_host(q_pinned.numpy(), tp, rp)
         rep_same = bool(np.array_equal(ids_r, ids_sh) and np.array_equal(d_r.view(np.uint32), d_sh.view(np.uint32)))
@@ -687,7 +700,8 @@ def sharded_leg(args, rank, world, local, device):
     dev_ms, e2e_ms, beam_ms, rep_ms, rep_beam_ms, rep_bad = [float(x) for x in times.cpu()]
     sums = torch.tensor([beam_bytes, rerank_bytes], dtype=torch.float64, device=device)
     dist.all_reduce(sums)
-    rec_t = torch.tensor([synth.recall_at_k(ids_sh, gt, 10) * (e - b), float(e - b)], dtype=torch.float64, device=device)
+    rec_t = torch.tensor([synth.recall_at_k(ids_sh[has_gt], gt, 10) * int(has_gt.sum()), float(has_gt.sum())],
+                         dtype=torch.float64, device=device)
     dist.all_reduce(rec_t)
     sr.close()
     dist.barrier()
@@ -704,9 +718,10 @@ def sharded_leg(args, rank, world, local, device):
     total_q = Q * world * args.steps
     return {
         "workload": (f"cfg4-style shards: {s.total_nodes} x {cfg.dim} uint8 over {world} GPUs ({s.rows_per_shard} per GPU), "
-                     f"R={degree}, PQ M={M}x256, RVQ entries=128, {Q} queries/batch per GPU, k=10, W=2; node ids scattered "
+                     f"R={degree}, PQ M={M}x256, RVQ 256x256 entries=128, {cfg.components} mixture components, {Q} queries/batch per GPU, k=10, W=2; node ids scattered "
                      f"so that {world - 1}/{world} of the row gathers are NVLink peer loads"),
-        "top_l": L, "rerank_top_n": top_n, "recall_at_10": round(float(rec_t[0] / rec_t[1]), 4), "sweep": sweep,
+        "top_l": L, "rerank_top_n": top_n, "recall_at_10": round(float(rec_t[0] / rec_t[1]), 4),
+        "recall_target_met": bool(float(rec_t[0] / rec_t[1]) >= RECALL_TARGET), "recall_queries": int(rec_t[1]), "sweep": sweep,
         "value": total_q / (dev_ms * 1e-3), "unit": "queries/s", "ms_per_step": dev_ms / args.steps,
         "e2e": {"value": total_q / (e2e_ms * 1e-3), "unit": "queries/s", "ms_per_step": e2e_ms / args.steps,
                 "h2d_bytes_per_step": int(Q * cfg.dim * 4), "d2h_bytes_per_step": int(world * Q * 10 * 8),
@@ -748,6 +763,14 @@ def main():
     device = f"cuda:{local}" if use_cuda else "cpu"
 
     from topoanns_b200 import synth
+    if args.sharded_only and world > 1 and args.impl == "b200":
+        rec = sharded_leg(args, rank, world, local, device)
+        if rank == 0:
+            print(json.dumps({"metric": "QPS at recall@10>=0.95 (uint8 d=128 index sharded by node-id range, 1 batch of 10k queries per GPU)",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "sharded": rec}))
+        import torch.distributed as dist
+        dist.destroy_process_group()
+        return 0
     s, build_s = build_index(args, device)
     gt = s.gt_ids.cpu().numpy()
     degree, M = s.adjacency.shape[1], s.pq_codes.shape[1]

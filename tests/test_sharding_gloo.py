@@ -87,6 +87,11 @@ def _sharded_worker(rank, world, port, out_path):
     sizes, offsets, ids = whole.rvq_buckets
     if int(sizes.sum()) != N or int(offsets[-1]) != ids.numel():
         problems.append("rvq buckets")
+    # ground truth for every fourth query only: the same index, the same rows where they are computed, -1 elsewhere
+    strided = synth_sharded.build(cfg, "cpu", gt_stride=4)
+    if not (torch.equal(strided.vectors, sh.vectors) and torch.equal(strided.gt_ids[::4], sh.gt_ids[::4])
+            and int(strided.gt_ids[1::4].max()) == -1 and int(strided.gt_ids[2::4].max()) == -1):
+        problems.append("strided ground truth")
     if rank == 0:
         host = pipeline.index_from_synth(whole)
         r = pipeline.run(host, whole.queries.numpy(), top_l=64, search_width=2, max_expansions=2048, top_n=64,

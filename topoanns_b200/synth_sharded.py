@@ -90,9 +90,11 @@ def _scatter_by_owner(rows: torch.Tensor, owner: torch.Tensor, local_row: torch.
     return out
 
 
-def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
+def build(cfg: synth.SynthConfig, device="cpu", gt_stride: int = 1) -> ShardedSynth:
     """cfg.num_nodes is the size of the WHOLE index; it is rounded down so that shards are equal and
-    page-aligned. Must be called by every rank of the process group."""
+    page-aligned. Must be called by every rank of the process group. With gt_stride > 1 the brute-force
+    ground truth is computed for every gt_stride-th query only (the other rows of gt_ids are -1): at a
+    billion vectors the exact neighbours of all queries cost more than the index."""
     world, rank = dist.get_world_size(), dist.get_rank()
     dev = torch.device(device)
     if dev.type == "cuda":
@@ -120,7 +122,6 @@ def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
         e = min(n_loc, s + step)
         comp_ids = rank * comps_loc + torch.arange(s, e, device=dev) // n_per
         grouped[s:e] = synth._sample_component(cfg, centres, comp_ids, own).to(out_dtype)
-    knn = synth.build_knn_graph(grouped, n_per, cfg.knn_edges)              # local row numbers
     a, b = _coprime_multiplier(n_tot), 12345 % n_tot
 
     def perm(x):  # old global id -> new global id
@@ -128,12 +129,31 @@ def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
 
     old = rank * n_loc + torch.arange(n_loc, device=dev, dtype=torch.int64)
     new = perm(old)
-    rand_edges = torch.randint(0, n_tot, (n_loc, cfg.random_edges), generator=own, device=dev)
-    adjacency = torch.cat([perm(rank * n_loc + knn), rand_edges], 1).to(torch.int32)
-    del knn, rand_edges
-    # PQ pivots from rank 0's sample, shared by everyone
-    sample = torch.randperm(n_loc, generator=own, device=dev)[:min(n_loc, cfg.train_sample)]
-    xs = grouped[sample].float()
+    if n_loc <= (1 << 25):
+        knn = synth.build_knn_graph(grouped, n_per, cfg.knn_edges)              # local row numbers
+        rand_edges = torch.randint(0, n_tot, (n_loc, cfg.random_edges), generator=own, device=dev)
+        adjacency = torch.cat([perm(rank * n_loc + knn), rand_edges], 1).to(torch.int32)
+        del knn, rand_edges
+    else:
+        # very large shards: slices of whole components, so that only a slice's 64-bit tables exist at a time
+        kk = min(cfg.knn_edges, n_per - 1)
+        adjacency = torch.empty((n_loc, kk + cfg.random_edges), dtype=torch.int32, device=dev)
+        slice_rows = max(1, (1 << 22) // n_per) * n_per
+        for lo in range(0, n_loc, slice_rows):
+            hi = min(n_loc, lo + slice_rows)
+            knn = synth.build_knn_graph(grouped[lo:hi], n_per, cfg.knn_edges) + lo
+            rnd = torch.randint(0, n_tot, (hi - lo, cfg.random_edges), generator=own, device=dev)
+            adjacency[lo:hi] = torch.cat([perm(rank * n_loc + knn), rnd], 1).to(torch.int32)
+            del knn, rnd
+    # training sample drawn from every rank's components (a rank holds its own components only at this point);
+    # rank 0 trains the PQ pivots and the entry model on it and shares them
+    take = min(n_loc, max(1, cfg.train_sample // world))
+    sample = torch.randperm(n_loc, generator=own, device=dev)[:take]
+    mine = grouped[sample].contiguous()
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    xs = torch.cat(parts).float()
+    del parts, mine
     if rank == 0:
         tables, centroid, offs = synth.train_pq(xs, cfg.pq_chunks, cfg.kmeans_iters, own)
     else:
@@ -165,7 +185,8 @@ def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
     adjacency = _scatter_by_owner(adjacency, owner, local_row, n_loc)
     codes = _scatter_by_owner(codes, owner, local_row, n_loc)
     # ground truth: local brute force, merged over ranks
-    loc_i, loc_d = synth.brute_force_topk(vectors, queries, cfg.top_k)
+    gt_rows = torch.arange(0, queries.shape[0], max(1, gt_stride), device=dev)
+    loc_i, loc_d = synth.brute_force_topk(vectors, queries[gt_rows], cfg.top_k)
     loc_i = loc_i + rank * n_loc
     all_i = [torch.empty_like(loc_i) for _ in range(world)]
     all_d = [torch.empty_like(loc_d) for _ in range(world)]
@@ -174,6 +195,10 @@ def build(cfg: synth.SynthConfig, device="cpu") -> ShardedSynth:
     cat_d, cat_i = torch.cat(all_d, 1), torch.cat(all_i, 1)
     order = torch.argsort(cat_d, dim=1, stable=True)[:, :cfg.top_k]
     gt = cat_i.gather(1, order)
+    if gt_stride > 1:
+        full = torch.full((queries.shape[0], cfg.top_k), -1, dtype=gt.dtype, device=dev)
+        full[gt_rows] = gt
+        gt = full
     out = ShardedSynth(cfg, world, rank, n_tot, n_loc, vectors, adjacency, codes, tables, centroid, offs, queries, gt)
     out.centres = centres
     if cfg.rvq:
