@@ -79,6 +79,9 @@ def parse_args():
     ap.add_argument("--shard-nodes", type=int, default=10_000_000,
                     help="N > 1: rows per GPU of the node-id-range-sharded leg (R = 32 records as in the 1 B-vector configuration)")
     ap.add_argument("--no-sharded-leg", action="store_true", help="N > 1: skip the node-id-range-sharded leg")
+    ap.add_argument("--shard-rvq-side", type=int, default=0,
+                    help="centroids per level of the sharded index's entry model (0: 256, doubled while a bucket "
+                         "would hold more than 640 nodes)")
     ap.add_argument("--shard-gt-stride", type=int, default=1,
                     help="N > 1: brute-force ground truth of the sharded leg for every n-th query only (very large shards)")
     ap.add_argument("--sharded-only", action="store_true",
@@ -508,9 +511,16 @@ def sharded_leg(args, rank, world, local, device):
     t0 = time.time()
     # Mixture components of 1000 nodes whatever the size of the index: larger components of this isotropic mixture
     # cannot be ranked by 32-byte PQ codes (4000-node components gave recall@10 0.58 with 2048 candidates reranked).
+    # The entry model follows the index: its posting lists stop at 256 ids and 128 of them are the entries, so a
+    # bucket of many more nodes hands out a thin sample of the query's region (256 x 256 on 82 M nodes, 1250 nodes
+    # per bucket: recall@10 levelled off at 0.946).
     total = args.shard_nodes * world
+    side = 256 if args.shard_rvq_side == 0 else args.shard_rvq_side
+    while args.shard_rvq_side == 0 and side * side * 640 < total and side < 4096:
+        side *= 2
     cfg = dataclasses.replace(synth.CONFIGS["cfg4"], num_nodes=total, num_queries=Q * world,
-                              components=max(world, total // 1000), kmeans_iters=5, train_sample=65536)
+                              components=max(world, total // 1000), kmeans_iters=5, train_sample=max(65536, 64 * side),
+                              rvq_coarse=side, rvq_fine=side)
     s = synth_sharded.build(cfg, device, gt_stride=max(1, args.shard_gt_stride))   # this rank's shard + all queries + ground truth
     torch.cuda.synchronize()
     build_s = time.time() - t0
@@ -549,7 +559,10 @@ def sharded_leg(args, rank, world, local, device):
         sweep.append(dict(top_l=L, rerank_top_n=tn, recall_at_10=round(float(agg[0] / agg[1]), 4),
                           qps_e2e=round(Q * world / float(worst), 1)))
     ok = [p for p in sweep if p["recall_at_10"] >= RECALL_TARGET]
-    chosen = max(ok, key=lambda p: p["qps_e2e"]) if ok else max(sweep, key=lambda p: (p["recall_at_10"], p["qps_e2e"]))
+    if not ok:   # recall has levelled off below the target: the fastest point within 0.005 of the best one
+        top = max(p["recall_at_10"] for p in sweep)
+        ok = [p for p in sweep if p["recall_at_10"] >= top - 0.005]
+    chosen = max(ok, key=lambda p: p["qps_e2e"])
     L, top_n = chosen["top_l"], chosen["rerank_top_n"]
     tp = search.TopologySearchParams(top_l=L, search_width=2, max_expansions=4096)
     rp = search.RerankExactParams(top_k=10, top_n=top_n)
@@ -718,7 +731,7 @@ def sharded_leg(args, rank, world, local, device):
     total_q = Q * world * args.steps
     return {
         "workload": (f"cfg4-style shards: {s.total_nodes} x {cfg.dim} uint8 over {world} GPUs ({s.rows_per_shard} per GPU), "
-                     f"R={degree}, PQ M={M}x256, RVQ 256x256 entries=128, {cfg.components} mixture components, {Q} queries/batch per GPU, k=10, W=2; node ids scattered "
+                     f"R={degree}, PQ M={M}x256, RVQ {side}x{side} entries=128, {cfg.components} mixture components, {Q} queries/batch per GPU, k=10, W=2; node ids scattered "
                      f"so that {world - 1}/{world} of the row gathers are NVLink peer loads"),
         "top_l": L, "rerank_top_n": top_n, "recall_at_10": round(float(rec_t[0] / rec_t[1]), 4),
         "recall_target_met": bool(float(rec_t[0] / rec_t[1]) >= RECALL_TARGET), "recall_queries": int(rec_t[1]), "sweep": sweep,

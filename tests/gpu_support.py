@@ -12,7 +12,7 @@ from topoanns_b200 import search, synth
 
 @functools.lru_cache(maxsize=8)
 def small_index(name="cfg1", num_nodes=20000, components=200, num_queries=256, seed=1234, pq_chunks=None,
-                knn_edges=None, random_edges=None, dim=None):
+                knn_edges=None, random_edges=None, dim=None, rvq_coarse=None, rvq_fine=None):
     base = synth.CONFIGS[name]
     kw = dict(num_nodes=num_nodes, components=components, num_queries=num_queries, seed=seed,
               train_sample=32768, kmeans_iters=8)
@@ -24,6 +24,10 @@ def small_index(name="cfg1", num_nodes=20000, components=200, num_queries=256, s
         kw["random_edges"] = random_edges
     if dim is not None:
         kw["dim"] = dim
+    if rvq_coarse is not None:
+        kw["rvq_coarse"] = rvq_coarse
+    if rvq_fine is not None:
+        kw["rvq_fine"] = rvq_fine
     cfg = dataclasses.replace(base, **kw)
     s = synth.build(cfg, "cuda" if torch.cuda.is_available() else "cpu")
     host = pipeline.index_from_synth(s)

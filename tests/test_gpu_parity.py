@@ -412,6 +412,20 @@ def test_rvq_entries_match_checker():
     assert np_u32(ids).tolist() == [[77, INVALID, INVALID, INVALID]] * 4
 
 
+@pytest.mark.parametrize("coarse,fine", [(512, 384), (258, 130)])
+def test_rvq_entries_with_codebooks_larger_than_shared_memory(coarse, fine):
+    # a 512-centroid level of 128 floats does not fit beside a query tile: the levels are streamed in tiles;
+    # sizes that are not multiples of 4 take the row-at-a-time kernel
+    s, host = small_index(name="cfg2", num_nodes=60000, components=60, num_queries=700, rvq_coarse=coarse, rvq_fine=fine)
+    assert host["rvq_coarse"].shape[0] == coarse and host["rvq_fine"].shape[0] == fine
+    model = search.rvq_model_from_synth(s)
+    q = s.queries.cuda().contiguous()
+    offs, ids, clusters = model.device_entry_batch(q, 128)
+    rc, _, _ = orc.rvq_clusters(s.queries.cpu().numpy(), host["rvq_coarse"], host["rvq_fine"], host["rvq_sizes"])
+    assert np.array_equal(clusters.cpu().numpy(), rc)
+    assert np.array_equal(np_u32(ids), orc.rvq_gather(rc, host["rvq_offsets"], host["rvq_ids"], 128))
+
+
 def test_rvq_clusters_agree_with_gemm_scores():
     """The reference scores RVQ levels with a cuBLAS FP32 GEMM (distance_kernel.cu:114-124), whose summation
     order is not published, so bit parity cannot be pinned there. This test measures the next best thing:
