@@ -361,6 +361,37 @@ def test_rerank_early_stop_matches_checker(min_prefix, patience):
     assert n2 == n_full and torch.equal(d2, d3) and torch.equal(i2, i3)
 
 
+@pytest.mark.parametrize("tile,top_k,top_n,float_queries", [(1, 1, 40, False), (16, 32, 160, False), (33, 10, 100, True),
+                                                             (64, 5, 300, False), (48, 10, 24, True), (64, 32, 512, True),
+                                                             (65, 10, 160, False)])
+def test_rerank_short_tiles_match_checker(tile, top_k, top_n, float_queries):
+    """Tiles of up to 64 ranks with top_k <= 32 are scored by one warp per query (tile 65: a block per query):
+    same lists, same count of exact distances as the checker, for one- and two-round tiles, lists that are not
+    powers of two and both query kinds."""
+    s, host = small_index()
+    ix = device_index(s)
+    Q = s.queries.shape[0]
+    eo, ei = fixed_entries(Q, [s.medoid])
+    L = max(top_n, 16)
+    p = search.TopologySearchParams(top_l=L, search_width=2, max_expansions=4096)
+    q8 = s.queries.cuda().to(torch.uint8).contiguous()
+    cand, _ = search.beam_search(ix, p, eo, ei, queries=q8, capacity=p.capacity(top_n))
+    if float_queries:
+        q = s.queries.cuda().float().contiguous() + 0.25     # not uint8-valued: float arithmetic on uint8 rows
+        q_np = q.cpu().numpy()
+    else:
+        q, q_np = q8, q8.cpu().numpy()
+    rp = search.RerankExactParams(top_k=top_k, top_n=top_n, rank_tile_size=tile, use_early_stop=True,
+                                  early_stop_min_prefix=2 * tile, early_stop_patience_tiles=2)
+    d, i, n_exact, _ = search.rerank_exact(ix, rp, cand, q)
+    rd, ri, rn, _ = orc.rerank(np_u32(cand), q_np, host_pages(host), np.uint8, top_n=top_n, top_k=top_k, tile=tile,
+                               vectors_per_page=host["vpp"], page_bytes=4096, vector_bytes=host["vb"],
+                               early_stop_min_prefix=2 * tile, early_stop_patience_tiles=2)
+    assert n_exact == rn
+    assert np.array_equal(np_u32(i), ri)
+    assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
+
+
 def test_rerank_int8_vectors():
     """Stored int8 vectors (the third scalar kind of the vector store) with int8 and float queries."""
     s, host = small_index()

@@ -49,14 +49,14 @@ __device__ __forceinline__ uint32_t SqDiffBytes(uint32_t a, uint32_t b, uint32_t
 }
 
 // Integer rows: kStep candidates per octet and step; dim / 16 sixteen-byte pieces per row.
-template <uint32_t kStep>
+template <uint32_t kStep, uint32_t kOctets>
 __device__ __forceinline__ void OctetRanksInt(unsigned long long* keys, const uint32_t* rank_ids,
                                               const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
                                               uint32_t octet, uint32_t ol) {
     const uint32_t pieces = dim / 16;
     // The loop bound is the warp's first octet, so all 32 lanes make the same number of trips (the
     // shuffles below need every lane); octets past the end carry invalid slots and write nothing.
-    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += kOctets * kStep) {
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         uint32_t acc[kStep];
@@ -95,13 +95,13 @@ __device__ __forceinline__ void OctetRanksInt(unsigned long long* keys, const ui
 }
 
 // Float rows with float queries, dim a multiple of 4.
-template <uint32_t kStep>
+template <uint32_t kStep, uint32_t kOctets>
 __device__ __forceinline__ void OctetRanksF32(unsigned long long* keys, const uint32_t* rank_ids,
                                               const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
                                               uint32_t octet, uint32_t ol) {
     // The loop bound is the warp's first octet, so all 32 lanes make the same number of trips (the
     // shuffles below need every lane); octets past the end carry invalid slots and write nothing.
-    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += kOctets * kStep) {
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         float acc[kStep][4];
@@ -147,11 +147,11 @@ __device__ __forceinline__ void OctetRanksF32(unsigned long long* keys, const ui
 
 // uint8 rows with float queries that are not uint8-valued: the same lane ownership as the float
 // rows, four bytes per lane and 32 dims.
-template <uint32_t kStep>
+template <uint32_t kStep, uint32_t kOctets>
 __device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const uint32_t* rank_ids,
                                                 const uint8_t* qrow, uint32_t dim, uint32_t begin, uint32_t end,
                                                 uint32_t octet, uint32_t ol) {
-    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += (kRerankThreads / 8) * kStep) {
+    for (uint32_t w0 = begin + (octet & ~3u) * kStep; w0 < end; w0 += kOctets * kStep) {
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         float acc[kStep][4];
@@ -203,26 +203,30 @@ struct ScoreMode {
 };
 
 // Exact distances of ranks [rb, end): keys[r] holds the address of rank r's vector (or the invalid
-// key) on entry and its (distance, id) sort key on return. Called by all threads of the block.
+// key) on entry and its (distance, id) sort key on return. Called by all kGroupThreads threads that
+// share the range (a block of kRerankThreads, or one warp); tid is the thread's number among them.
+template <uint32_t kGroupThreads>
 __device__ __forceinline__ void ScoreRanks(const TannIndexView& ix, const ScoreMode& m, unsigned long long* keys,
-                                           const uint32_t* rank_ids, const uint8_t* qrow, uint32_t rb, uint32_t end) {
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+                                           const uint32_t* rank_ids, const uint8_t* qrow, uint32_t rb, uint32_t end,
+                                           uint32_t tid) {
+    constexpr uint32_t kOct = kGroupThreads / 8;
+    const uint32_t lane = tid & 31, warp = tid >> 5;
     const uint32_t dim = ix.dim, rc = end - rb, qkind = m.qkind;
     const bool int_path = m.int_path, octet_int = m.octet_int, octet_f32 = m.octet_f32, octet_u8f32 = m.octet_u8f32;
     if (octet_int) {
-        if (rc >= 64) OctetRanksInt<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-        else OctetRanksInt<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        if (rc >= 64) OctetRanksInt<4, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksInt<2, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
     } else if (octet_f32) {
-        if (rc >= 64) OctetRanksF32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-        else OctetRanksF32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        if (rc >= 64) OctetRanksF32<4, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksF32<2, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
     } else if (octet_u8f32) {
-        if (rc >= 64) OctetRanksU8F32<4>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
-        else OctetRanksU8F32<2>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        if (rc >= 64) OctetRanksU8F32<4, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
+        else OctetRanksU8F32<2, kOct>(keys, rank_ids, qrow, dim, rb, end, tid >> 3, lane & 7);
     } else {
         // A warp scores kGroup candidates per step: all their row loads are issued before any
         // reduction, so several random reads are in flight per lane.
         constexpr uint32_t kGroup = 4;
-        for (uint32_t r0 = rb + warp * kGroup; r0 < end; r0 += (kRerankThreads / 32) * kGroup) {
+        for (uint32_t r0 = rb + warp * kGroup; r0 < end; r0 += (kGroupThreads / 32) * kGroup) {
             const uint8_t* vptr[kGroup];
             bool act[kGroup];
 #pragma unroll
@@ -377,7 +381,7 @@ rerank_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, cons
             if (lane == 0 && n_flt) atomicAdd(&s_filtered, n_flt);
             __syncthreads();
             // ---- distances --------------------------------------------------------------------
-            ScoreRanks(ix, mode, keys, rank_ids, qrow, rb, rb + rc);
+            ScoreRanks<kRerankThreads>(ix, mode, keys, rank_ids, qrow, rb, rb + rc, tid);
             __syncthreads();
             if (track_kth) {
                 // k-th smallest exact distance over ranks [0, rb + rc) (:541-571): the sorted best-k list is
@@ -647,7 +651,7 @@ rerank_learned_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams
             if (lane == 0 && n_flt) atomicAdd(&s_filtered, n_flt);
             s_top[cur ^ 1][tid] = kInvalidKey64;
             __syncthreads();
-            ScoreRanks(ix, mode, keys, rank_ids, qrow, rb, re);
+            ScoreRanks<kRerankThreads>(ix, mode, keys, rank_ids, qrow, rb, re, tid);
             __syncthreads();
             // ---- merge the window into the top_k list (:945-965) ---------------------------------
             {
@@ -763,6 +767,411 @@ rerank_learned_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams
     }
 }
 
+// The same rerank with one WARP per query (top_k <= 32, lists of at most kWarpFormMaxRanks ranks): the windows of
+// the schedule are 16 to 64 ranks wide, which leaves three warps of a block waiting at every barrier of the
+// block-per-query form; here the four warps of a block work on four queries and meet at no barrier. Every lane
+// holds the query's control state (all lanes compute it from the same values); the head probe of the next window
+// is spread over the lanes (a count and a minimum, both independent of the order).
+constexpr uint32_t kWarpFormWarps = 4;
+constexpr uint32_t kWarpFormMaxRanks = 512;
+
+__host__ __device__ inline size_t WarpFormBytes(uint32_t padded, size_t qbytes) {
+    return (((size_t)padded * 12 + 15) & ~(size_t)15) + ((qbytes + 15) & ~(size_t)15) + 2 * 32 * 8;
+}
+
+__global__ void __launch_bounds__(kWarpFormWarps * 32, 8)
+rerank_learned_warp_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p,
+                           const __grid_constant__ TannRerankLearnedStop ls, uint32_t use_schedule, uint32_t evaluate,
+                           const Cand* __restrict__ cand, uint32_t capacity, uint64_t Q, const void* __restrict__ queries,
+                           uint32_t qkind, const float* __restrict__ error_bounds, const uint32_t* __restrict__ replay,
+                           uint32_t padded, float* __restrict__ out_dists, uint32_t* __restrict__ out_ids,
+                           unsigned long long* __restrict__ out_counts, uint32_t* __restrict__ out_stop_prefixes,
+                           uint32_t* __restrict__ out_checkpoints, uint32_t* __restrict__ out_stop_flags,
+                           uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char rr_smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t dim = ix.dim, k = p.top_k;
+    const uint32_t qbytes = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
+    unsigned char* mine = rr_smem + (size_t)warp * WarpFormBytes(padded, qbytes);
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(mine);      // [padded]
+    uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
+    uint8_t* qrow = mine + (((size_t)padded * 12 + 15) & ~(size_t)15);
+    unsigned long long* top = reinterpret_cast<unsigned long long*>(qrow + ((qbytes + 15) & ~15u));   // [2][32]
+    const uint32_t budget = min(p.top_n, capacity);
+    const uint32_t tile = p.tile == 0 ? budget : p.tile;
+    const float kInf = __int_as_float(0x7f800000);
+    ScoreMode mode;
+    mode.qkind = qkind;
+    mode.int_path = qkind == TANN_KIND_UINT8 && ix.vector_kind == TANN_KIND_UINT8 && (dim % 4 == 0) && dim <= 256 &&
+                    (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0);
+    const bool rows16 = (ix.vector_bytes % 16 == 0) && (ix.page_bytes % 16 == 0);
+    mode.octet_int = mode.int_path && rows16 && (dim % 16 == 0);
+    mode.octet_f32 = !mode.int_path && rows16 && ix.vector_kind == TANN_KIND_FLOAT32 && qkind == TANN_KIND_FLOAT32 &&
+                     (dim % 4 == 0);
+    mode.octet_u8f32 = !mode.int_path && ix.vector_kind == TANN_KIND_UINT8 && qkind == TANN_KIND_FLOAT32 &&
+                       (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0) && (dim % 4 == 0);
+    unsigned long long tot_exact = 0, tot_filtered = 0;
+
+    for (uint64_t q = (uint64_t)blockIdx.x * kWarpFormWarps + warp; q < Q; q += (uint64_t)gridDim.x * kWarpFormWarps) {
+        const uint8_t* qsrc = static_cast<const uint8_t*>(queries) + q * qbytes;
+        __syncwarp();   // the previous query's reads of this warp's buffers are done
+        if (qbytes % 16 == 0) {
+            for (uint32_t i = lane; i < qbytes / 16; i += 32)
+                reinterpret_cast<uint4*>(qrow)[i] = __ldg(reinterpret_cast<const uint4*>(qsrc) + i);
+        } else {
+            for (uint32_t i = lane; i < qbytes; i += 32) qrow[i] = qsrc[i];
+        }
+        top[lane] = kInvalidKey64;
+        float kth_now = kInf, prev_ckpt_kth = kInf, prev_delta = 0.0f, qnorm = 0.0f;
+        uint32_t n_exact = 0, n_filtered = 0, stable = 0, stop = 0, stage = ls.initial_stage_index;
+        uint32_t next = use_schedule ? min(budget, ls.bootstrap_prefix) : min(budget, tile);
+        uint32_t ckpt = 0, stop_prefix = budget, has_prev = 0;
+        __syncwarp();
+        if (p.use_bound_filter) {
+            double sum = 0.0;
+            if (lane == 0) {
+                for (uint32_t i = 0; i < dim; ++i) {
+                    const double v = (double)LoadAsFloat<float>(qrow, qkind, i);
+                    sum += v * v;
+                }
+            }
+            qnorm = __shfl_sync(kFull, (float)sum, 0);
+        }
+        uint32_t cur = 0, exact_before = 0;
+        for (uint32_t rb = 0; rb < budget;) {
+            if (stop) break;
+            const uint32_t re = use_schedule ? next : min(budget, rb + tile);
+            const uint32_t rc = re - rb;
+            const float threshold = kth_now;
+            // ---- one lane per rank: candidate record, bound filter, vector address -----------------
+            uint32_t n_act = 0, n_flt = 0;
+            for (uint32_t r = rb + lane; r < re; r += 32) {
+                unsigned long long slot = kInvalidKey64;
+                const Cand c = cand[q * capacity + r];
+                const uint32_t id = c.id & kRawMask;
+                if (c.id != kInvalid && id >= ix.num_nodes && status != nullptr)
+                    atomicOr(status, TANN_STATUS_RERANK_ID_RANGE);   // skipped, and reported
+                if (c.id != kInvalid && id < ix.num_nodes) {
+                    bool keep = true;
+                    if (p.use_bound_filter && isfinite(threshold))
+                        keep = !(LowerBoundSq(c.dist - qnorm, __ldg(error_bounds + id)) > threshold);
+                    if (keep) {
+                        slot = reinterpret_cast<unsigned long long>(VectorPtr(ix, id));
+                        rank_ids[r] = id;
+                        ++n_act;
+                    } else {
+                        ++n_flt;
+                    }
+                }
+                keys[r] = slot;
+            }
+            n_exact += __reduce_add_sync(kFull, n_act);
+            n_filtered += __reduce_add_sync(kFull, n_flt);
+            unsigned long long* old_list = top + cur * 32;
+            unsigned long long* new_list = top + (cur ^ 1) * 32;
+            new_list[lane] = kInvalidKey64;
+            __syncwarp();
+            ScoreRanks<32>(ix, mode, keys, rank_ids, qrow, rb, re, lane);
+            __syncwarp();
+            // ---- merge the window into the top_k list by counting ------------------------------------
+            uint32_t entered = 0;
+            for (uint32_t t = lane; t < rc; t += 32) {
+                const unsigned long long e = keys[rb + t];
+                if (e == kInvalidKey64) continue;
+                uint32_t cnt = 0;
+                for (uint32_t u = 0; u < rc; ++u) {
+                    const unsigned long long x = keys[rb + u];
+                    cnt += (x < e || (x == e && u < t)) ? 1u : 0u;
+                }
+                for (uint32_t j = 0; j < k; ++j) cnt += old_list[j] <= e ? 1u : 0u;
+                if (cnt < k) {
+                    new_list[cnt] = e;
+                    ++entered;
+                }
+            }
+            if (lane < k) {
+                const unsigned long long x = old_list[lane];
+                if (x != kInvalidKey64) {
+                    uint32_t pos = lane;
+                    for (uint32_t u = 0; u < rc; ++u) pos += keys[rb + u] < x ? 1u : 0u;
+                    if (pos < k) new_list[pos] = x;
+                }
+            }
+            entered = __reduce_add_sync(kFull, entered);
+            __syncwarp();
+            cur ^= 1;
+            // ---- the stage boundary, by every lane alike -----------------------------------------------
+            {
+                const float previous_window_kth = KeyDist(old_list[k - 1]);
+                const uint32_t processed = re;
+                const float kth = KeyDist(new_list[k - 1]);
+                const uint32_t window_exact = n_exact - exact_before;
+                exact_before = n_exact;
+                kth_now = kth;
+                uint32_t stop_here = 0;
+                if (evaluate && ls.enabled != 0u && isfinite(kth) && stage < ls.num_stages &&
+                    processed >= ls.stage_prefixes[stage]) {
+                    const float delta_last = has_prev ? (prev_ckpt_kth - kth) : 0.0f;
+                    const float spread = kth - KeyDist(new_list[0]);
+                    uint32_t nwe = (stage + 1u < ls.num_stages) ? min(budget, ls.stage_prefixes[stage + 1u])
+                                                                : min(budget, re + tile);
+                    if (nwe < re) nwe = re;
+                    nwe = min(nwe, re + (uint32_t)TANN_RERANK_STOP_HEAD_PROBE);
+                    uint32_t live = 0;
+                    float best_lb = kInf;
+                    if (ls.linear_weights[8] != 0.0f || ls.linear_weights[9] != 0.0f) {
+                        for (uint32_t r = re + lane; r < nwe; r += 32) {
+                            const Cand c = cand[q * capacity + r];
+                            const uint32_t id = c.id & kRawMask;
+                            float lb = kInf;
+                            if (c.id != kInvalid && id < ix.num_nodes)
+                                lb = LowerBoundSq(c.dist - qnorm, __ldg(error_bounds + id));
+                            if (lb <= kth) {
+                                ++live;
+                                best_lb = fminf(best_lb, lb);
+                            }
+                        }
+                        live = __reduce_add_sync(kFull, live);
+#pragma unroll
+                        for (int off = 16; off >= 1; off >>= 1) best_lb = fminf(best_lb, __shfl_xor_sync(kFull, best_lb, off));
+                    }
+                    const float logit = RerankStopLogit(ls, processed, kth, delta_last, prev_delta,
+                                                        entered == 0u ? 0.0f : 1.0f, entered, spread, live, nwe - re,
+                                                        best_lb, window_exact, rc, n_exact);
+                    ++ckpt;
+                    if (logit < ls.threshold_logit) stop_here = 1;
+                    prev_ckpt_kth = kth;
+                    prev_delta = delta_last;
+                    has_prev = 1;
+                    ++stage;
+                } else if (replay != nullptr) {
+                    while (stage < ls.num_stages && ls.stage_prefixes[stage] <= processed) ++stage;
+                    if (processed >= replay[q]) stop_here = 1;
+                } else if (p.use_early_stop && processed >= p.early_stop_min_prefix && isfinite(kth)) {
+                    if (kth < previous_window_kth) stable = 0; else ++stable;
+                    if (stable >= p.early_stop_patience_tiles) stop_here = 1;
+                }
+                if (stop_here) {
+                    stop = 1;
+                    stop_prefix = processed;
+                } else if (use_schedule) {
+                    next = stage < ls.num_stages ? min(budget, ls.stage_prefixes[stage]) : min(budget, processed + tile);
+                }
+            }
+            __syncwarp();   // the old list is the next window's new list
+            rb = re;
+        }
+        if (lane < k) {
+            const unsigned long long key = top[cur * 32 + lane];
+            out_dists[q * k + lane] = KeyDist(key);
+            out_ids[q * k + lane] = (uint32_t)key;
+        }
+        if (lane == 0) {
+            tot_exact += n_exact;
+            tot_filtered += n_filtered;
+            if (out_stop_prefixes != nullptr) out_stop_prefixes[q] = stop_prefix;
+            if (out_checkpoints != nullptr) out_checkpoints[q] = ckpt;
+            if (out_stop_flags != nullptr) out_stop_flags[q] = stop;
+        }
+    }
+    if (lane == 0 && out_counts != nullptr) {
+        if (tot_exact) atomicAdd(out_counts, tot_exact);
+        if (tot_filtered) atomicAdd(out_counts + 1, tot_filtered);
+    }
+}
+
+// rerank_kernel's tiled form (bound filter and/or early stop, tiles of at most kWarpFormMaxTile ranks, top_k <= 32)
+// with one warp per query: a 16-rank tile keeps half a warp busy and a block of four warps would spend its time at
+// the five barriers of every tile. Same values as the block form: the tile is merged into the sorted best-k
+// distances by counting, the threshold of the next tile is their k-th, the final order is (distance, id).
+constexpr uint32_t kWarpFormMaxTile = 64;
+
+__global__ void __launch_bounds__(kWarpFormWarps * 32, 8)
+rerank_warp_kernel(const __grid_constant__ TannIndexView ix, TannRerankParams p, const Cand* __restrict__ cand,
+                   uint32_t capacity, uint64_t Q, const void* __restrict__ queries, uint32_t qkind,
+                   const float* __restrict__ error_bounds, uint32_t padded, float* __restrict__ out_dists,
+                   uint32_t* __restrict__ out_ids, unsigned long long* __restrict__ out_counts,
+                   const uint8_t* __restrict__ queries_u8, const uint32_t* __restrict__ not_u8_flag,
+                   uint32_t final_ranks, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char rr_smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t dim = ix.dim, k = p.top_k;
+    const bool as_u8 = qkind == TANN_KIND_UINT8 || (queries_u8 != nullptr && not_u8_flag != nullptr && *not_u8_flag == 0u);
+    const bool int_path = as_u8 && ix.vector_kind == TANN_KIND_UINT8 && (dim % 4 == 0) && dim <= 256 &&
+                          (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0);
+    // the buffers are laid out for the caller's query kind; the uint8 copy is never the larger one
+    const uint32_t qbytes_layout = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
+    if (int_path && qkind != TANN_KIND_UINT8) { queries = queries_u8; qkind = TANN_KIND_UINT8; }
+    const uint32_t qbytes = dim * (qkind == TANN_KIND_FLOAT32 ? 4u : 1u);
+    unsigned char* mine = rr_smem + (size_t)warp * WarpFormBytes(padded, qbytes_layout);
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(mine);      // [padded]
+    uint32_t* rank_ids = reinterpret_cast<uint32_t*>(keys + padded);              // [padded]
+    uint8_t* qrow = mine + (((size_t)padded * 12 + 15) & ~(size_t)15);
+    float* best = reinterpret_cast<float*>(qrow + ((qbytes_layout + 15) & ~15u));   // [2][32] sorted best-k distances
+    float* tl = best + 64;                                                          // [64] a tile's distances
+    const uint32_t tile = p.tile;
+    const float kInf = __int_as_float(0x7f800000);
+    const bool rows16 = (ix.vector_bytes % 16 == 0) && (ix.page_bytes % 16 == 0);
+    const bool octet_int = int_path && rows16 && (dim % 16 == 0);
+    const bool octet_f32 = !int_path && rows16 && ix.vector_kind == TANN_KIND_FLOAT32 &&
+                           qkind == TANN_KIND_FLOAT32 && (dim % 4 == 0);
+    const bool octet_u8f32 = !int_path && ix.vector_kind == TANN_KIND_UINT8 && qkind == TANN_KIND_FLOAT32 &&
+                             (ix.vector_bytes % 4 == 0) && (ix.page_bytes % 4 == 0) && (dim % 4 == 0);
+    const ScoreMode mode{int_path, octet_int, octet_f32, octet_u8f32, qkind};
+    unsigned long long tot_exact = 0, tot_filtered = 0;
+
+    for (uint64_t q = (uint64_t)blockIdx.x * kWarpFormWarps + warp; q < Q; q += (uint64_t)gridDim.x * kWarpFormWarps) {
+        const uint8_t* qsrc = static_cast<const uint8_t*>(queries) + q * qbytes;
+        __syncwarp();   // the previous query's reads of this warp's buffers are done
+        if (qbytes % 16 == 0) {
+            for (uint32_t i = lane; i < qbytes / 16; i += 32)
+                reinterpret_cast<uint4*>(qrow)[i] = __ldg(reinterpret_cast<const uint4*>(qsrc) + i);
+        } else {
+            for (uint32_t i = lane; i < qbytes; i += 32) qrow[i] = qsrc[i];
+        }
+        for (uint32_t i = lane; i < padded; i += 32) keys[i] = kInvalidKey64;
+        best[lane] = kInf;
+        float threshold = kInf, prev_kth = kInf, qnorm = 0.0f;
+        uint32_t n_exact = 0, n_filtered = 0, stable = 0, cur = 0;
+        __syncwarp();
+        if (p.use_bound_filter) {
+            double sum = 0.0;
+            if (lane == 0) {
+                for (uint32_t i = 0; i < dim; ++i) {
+                    const double v = (double)LoadAsFloat<float>(qrow, qkind, i);
+                    sum += v * v;
+                }
+            }
+            qnorm = __shfl_sync(kFull, (float)sum, 0);
+        }
+        for (uint32_t rb = 0; rb < p.top_n; rb += tile) {
+            const uint32_t rc = min(tile, p.top_n - rb);
+            uint32_t n_act = 0, n_flt = 0;
+            for (uint32_t r = rb + lane; r < rb + rc; r += 32) {
+                unsigned long long slot = kInvalidKey64;
+                if (r < capacity) {
+                    const Cand c = cand[q * capacity + r];
+                    const uint32_t id = c.id & kRawMask;
+                    if (c.id != kInvalid && id >= ix.num_nodes && status != nullptr)
+                        atomicOr(status, TANN_STATUS_RERANK_ID_RANGE);   // skipped, and reported
+                    if (c.id != kInvalid && id < ix.num_nodes) {
+                        bool keep = true;
+                        if (p.use_bound_filter && isfinite(threshold))
+                            keep = !(LowerBoundSq(c.dist - qnorm, __ldg(error_bounds + id)) > threshold);
+                        if (keep) {
+                            slot = reinterpret_cast<unsigned long long>(VectorPtr(ix, id));
+                            rank_ids[r] = id;
+                            ++n_act;
+                        } else {
+                            ++n_flt;
+                        }
+                    }
+                }
+                keys[r] = slot;
+            }
+            n_exact += __reduce_add_sync(kFull, n_act);
+            n_filtered += __reduce_add_sync(kFull, n_flt);
+            __syncwarp();
+            ScoreRanks<32>(ix, mode, keys, rank_ids, qrow, rb, rb + rc, lane);
+            __syncwarp();
+            // ---- the tile's distances merged into the best-k list by counting ---------------------------
+            const float* old_best = best + cur * 32;
+            float* new_best = best + (cur ^ 1) * 32;
+            for (uint32_t t = lane; t < rc; t += 32) tl[t] = FromOrderedBits((uint32_t)(keys[rb + t] >> 32));
+            __syncwarp();
+            if (lane < k) {
+                const float oldv = old_best[lane];
+                uint32_t c_old = 0;
+                for (uint32_t l = 0; l < rc; ++l) c_old += tl[l] < oldv ? 1u : 0u;
+                if (lane + c_old < k) new_best[lane + c_old] = oldv;
+            }
+            for (uint32_t t = lane; t < rc; t += 32) {
+                const float newv = tl[t];
+                uint32_t c_new = 0;
+                for (uint32_t l = 0; l < rc; ++l) {
+                    const float x = tl[l];
+                    c_new += (x < newv || (x == newv && l < t)) ? 1u : 0u;
+                }
+                uint32_t lo = 0;   // old entries <= newv
+#pragma unroll
+                for (uint32_t b = 32; b > 0; b >>= 1) {
+                    const uint32_t u = lo + b;
+                    if (u <= k && old_best[u - 1] <= newv) lo = u;
+                }
+                if (lo + c_new < k) new_best[lo + c_new] = newv;
+            }
+            __syncwarp();
+            cur ^= 1;
+            const float kth = new_best[k - 1];
+            threshold = kth;
+            bool stop = false;
+            if (p.use_early_stop) {   // src/io/bam_vector_provider.cu:1124-1135
+                if (rb + rc >= p.early_stop_min_prefix && isfinite(kth)) {
+                    if (kth < prev_kth) stable = 0; else ++stable;
+                    if (stable >= p.early_stop_patience_tiles) stop = true;
+                }
+                prev_kth = kth;
+            }
+            __syncwarp();   // the old list is the next tile's new list
+            if (stop) break;
+        }
+        // ---- final order ---------------------------------------------------------------------------------
+        uint32_t out_n = p.top_n;
+        if (final_ranks != 0 && final_ranks <= 32 && padded >= 64) {
+            // the 32 smallest keys: every run of 32 sorted, then folded one after another into the running best 32
+            unsigned long long m = WarpSortKey(keys[lane], lane);
+            for (uint32_t c = 1; c < padded / 32; ++c) {
+                unsigned long long kb = WarpSortKey(keys[c * 32 + lane], lane);
+                kb = __shfl_sync(kFull, kb, 31 - lane);
+                m = m < kb ? m : kb;
+#pragma unroll
+                for (uint32_t sft = 16; sft > 0; sft >>= 1) {
+                    const unsigned long long o = __shfl_xor_sync(kFull, m, sft);
+                    const bool upper = (lane & sft) != 0;
+                    m = upper ? (o > m ? o : m) : (o < m ? o : m);
+                }
+            }
+            keys[lane] = m;
+            out_n = min(p.top_n, 32u);
+        } else {
+            uint32_t first_k = 2;
+            if (padded >= 64) {
+                for (uint32_t c = 0; c < padded / 32; ++c) {
+                    unsigned long long key = WarpSortKey(keys[c * 32 + lane], lane);
+                    if (c & 1u) key = __shfl_sync(kFull, key, 31 - lane);   // odd runs descending, as the network expects
+                    keys[c * 32 + lane] = key;
+                }
+                first_k = 64;
+                __syncwarp();
+            }
+            for (uint32_t kk = first_k; kk <= padded; kk <<= 1) {
+                for (uint32_t j = kk >> 1; j > 0; j >>= 1) {
+                    for (uint32_t t = lane; t < padded / 2; t += 32) {
+                        const uint32_t lo = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                        const uint32_t hi = lo | j;
+                        const bool asc = (lo & kk) == 0;
+                        const unsigned long long a = keys[lo], b = keys[hi];
+                        if ((a > b) == asc) { keys[lo] = b; keys[hi] = a; }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        __syncwarp();
+        for (uint32_t i = lane; i < out_n; i += 32) {
+            const unsigned long long key = keys[i];
+            out_dists[q * p.top_n + i] = FromOrderedBits((uint32_t)(key >> 32));
+            out_ids[q * p.top_n + i] = (uint32_t)key;
+        }
+        tot_exact += n_exact;
+        tot_filtered += n_filtered;
+    }
+    if (lane == 0 && out_counts != nullptr) {
+        if (tot_exact) atomicAdd(out_counts, tot_exact);
+        if (tot_filtered) atomicAdd(out_counts + 1, tot_filtered);
+    }
+}
+
 __global__ void topk_pack_kernel(const float* __restrict__ dists, const uint32_t* __restrict__ ids,
                                  uint64_t Q, uint32_t top_n, uint32_t top_k,
                                  float* __restrict__ out_dists, uint32_t* __restrict__ out_ids) {
@@ -786,6 +1195,21 @@ cudaError_t LaunchRerank(const TannIndexView& ix, const TannRerankParams& p, con
     uint32_t padded = 1;
     while (padded < p.top_n) padded <<= 1;
     const size_t qbytes = (size_t)ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
+    if ((p.use_bound_filter || p.use_early_stop) && p.tile != 0 && p.tile <= kWarpFormMaxTile && p.top_k <= 32 &&
+        p.top_k != 0 && padded <= kWarpFormMaxRanks) {   // short tiles: one warp per query
+        const size_t smem_w = WarpFormBytes(padded, qbytes) * kWarpFormWarps;
+        if (smem_w > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(rerank_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem_w);
+            if (e != cudaSuccess) return e;
+        }
+        const uint64_t blocks = (Q + kWarpFormWarps - 1) / kWarpFormWarps;
+        const uint64_t cap_w = (uint64_t)SmCount() * 8;
+        rerank_warp_kernel<<<(unsigned)(blocks < cap_w ? blocks : cap_w), kWarpFormWarps * 32, smem_w, stream>>>(
+            ix, p, static_cast<const Cand*>(cand), capacity, Q, queries, query_kind, error_bounds, padded,
+            out_dists, out_ids, out_counts, queries_u8, not_u8_flag, final_ranks, status);
+        return cudaGetLastError();
+    }
     const size_t smem = (((size_t)padded * 12 + 15) & ~(size_t)15) + ((qbytes + 15) & ~(size_t)15);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(rerank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -811,6 +1235,21 @@ cudaError_t LaunchRerankLearned(const TannIndexView& ix, const TannRerankParams&
     uint32_t padded = 1;
     while (padded < budget) padded <<= 1;
     const size_t qbytes = (size_t)ix.dim * (query_kind == TANN_KIND_FLOAT32 ? 4 : 1);
+    if (p.top_k <= 32 && padded <= kWarpFormMaxRanks) {   // one warp per query
+        const size_t smem = WarpFormBytes(padded, qbytes) * kWarpFormWarps;
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(rerank_learned_warp_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+        }
+        const uint64_t blocks = (Q + kWarpFormWarps - 1) / kWarpFormWarps;
+        const uint64_t cap = (uint64_t)SmCount() * 8;
+        rerank_learned_warp_kernel<<<(unsigned)(blocks < cap ? blocks : cap), kWarpFormWarps * 32, smem, stream>>>(
+            ix, p, model, use_schedule ? 1u : 0u, evaluate ? 1u : 0u, static_cast<const Cand*>(cand), capacity, Q,
+            queries, query_kind, error_bounds, replay_stop_prefixes, padded, out_dists, out_ids, out_counts,
+            out_stop_prefixes, out_checkpoint_counts, out_stop_flags, status);
+        return cudaGetLastError();
+    }
     const size_t smem = (((size_t)padded * 12 + 15) & ~(size_t)15) + ((qbytes + 15) & ~(size_t)15);
     if (smem > 40 * 1024) {   // the kernel also has 2 KB of static shared memory
         cudaError_t e = cudaFuncSetAttribute(rerank_learned_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
