@@ -668,6 +668,8 @@ def sharded_leg(args, rank, world, local, device):
     # adjacency rows and vector pages stay sharded ------------------------------------------------------------
     rep_ms = rep_beam_ms = 0.0
     rep_same = True
+    own_ms = own_e2e_ms = 0.0
+    own_same, own_slot, own_over = True, 0, False
     if s.total_nodes * M <= 40e9:
         parts = [torch.empty_like(s.pq_codes) for _ in range(world)]
         dist.all_gather(parts, s.pq_codes.contiguous())
@@ -705,12 +707,64 @@ def sharded_leg(args, rank, world, local, device):
         barrier()
         rep_beam_ms = r0.elapsed_time(r1) / args.steps
         sr_r.close()
+        # ---- the same, and the exact rerank done by the owner of the rows: the candidate lists are split by owner
+        # and exchanged (all-to-all), every GPU scores what it received against its own shard, the [Q, 10] lists
+        # travel back and are merged - no vector row crosses NVLink ------------------------------------------------
+        local_ix = dataclasses.replace(ix, num_nodes=s.rows_per_shard, codes=None, rows_per_shard=0,
+                                       adjacency_bases=[ix.adjacency_bases[rank]], codes_bases=[ix.codes_bases[rank]],
+                                       vector_bases=[ix.vector_bases[rank]])
+        orr = sharding.OwnerRerank(local_ix, s.rows_per_shard, Q, top_n, 10, q_devs[0].dtype)
+        own_slot = orr.slot
+        cap_o = tp.capacity(top_n)
+
+        def owner_step(qd):
+            eo, ei, _ = model.device_entry_batch(qd, 128)
+            cand_o, _ = search.beam_search(ix_r, tp, eo, ei, queries=qd, capacity=cap_o)
+            return orr.run(cand_o, qd)
+
+        oi, od = owner_step(q_devs[0])
+        torch.cuda.synchronize()
+        own_same = bool(np.array_equal(oi.cpu().numpy().view(np.uint32), ids_sh.view(np.uint32)) and
+                        np.array_equal(od.cpu().numpy().view(np.uint32), d_sh.view(np.uint32)))
+        for i in range(args.warmup):
+            owner_step(q_devs[i % nb])
+        barrier()
+        r0.record(stream)
+        for i in range(args.steps):
+            owner_step(q_devs[i % nb])
+        r1.record(stream)
+        barrier()
+        own_ms = r0.elapsed_time(r1)
+
+        def owner_e2e_step(i):
+            q_in.copy_(q_pins[i % nb], non_blocking=True)
+            oi, od = owner_step(q_in)
+            packed[:, :10] = oi
+            packed[:, 10:] = od.view(torch.int32)
+            dist.gather(packed, gathered, dst=0)
+            if rank == 0:
+                for r in range(world):
+                    out_pinned[r].copy_(gathered[r], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for i in range(args.warmup):
+            owner_e2e_step(i)
+        barrier()
+        t1 = time.perf_counter()
+        for i in range(args.steps):
+            owner_e2e_step(i)
+        torch.cuda.synchronize()
+        own_e2e_ms = (time.perf_counter() - t1) * 1000.0
+        barrier()
+        own_over = orr.overflowed()
+        del orr, local_ix
         del all_codes, ix_r
         torch.cuda.empty_cache()
-    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms, rep_ms, rep_beam_ms, 0.0 if rep_same else 1.0], dtype=torch.float64,
-                         device=device)
+    times = torch.tensor([dev_ms, e2e_s * 1000.0, beam_ms, rep_ms, rep_beam_ms, 0.0 if rep_same else 1.0, own_ms, own_e2e_ms,
+                          0.0 if own_same else 1.0, 1.0 if own_over else 0.0], dtype=torch.float64, device=device)
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms, beam_ms, rep_ms, rep_beam_ms, rep_bad = [float(x) for x in times.cpu()]
+    dev_ms, e2e_ms, beam_ms, rep_ms, rep_beam_ms, rep_bad, own_ms, own_e2e_ms, own_bad, own_overflow = \
+        [float(x) for x in times.cpu()]
     sums = torch.tensor([beam_bytes, rerank_bytes], dtype=torch.float64, device=device)
     dist.all_reduce(sums)
     rec_t = torch.tensor([synth.recall_at_k(ids_sh[has_gt], gt, 10) * int(has_gt.sum()), float(has_gt.sum())],
@@ -749,6 +803,14 @@ def sharded_leg(args, rank, world, local, device):
                     "HBM, adjacency rows and vector pages stay sharded",
             "value": total_q / (rep_ms * 1e-3), "unit": "queries/s", "ms_per_step": rep_ms / args.steps,
             "beam_kernel_ms": round(rep_beam_ms, 4), "results_identical_to_sharded_codes": rep_bad == 0.0}),
+        "codes_replicated_rerank_by_owner": (None if own_ms == 0.0 else {
+            "what": "PQ codes replicated as above, and the exact rerank done by the owner of the rows: candidate lists split "
+                    "by owner and exchanged (NCCL all-to-all), scored against the local shard, [Q, 10] lists returned "
+                    "(all-to-all) and merged; no vector row crosses NVLink",
+            "value": total_q / (own_ms * 1e-3), "unit": "queries/s", "ms_per_step": own_ms / args.steps,
+            "e2e": {"value": total_q / (own_e2e_ms * 1e-3), "unit": "queries/s", "ms_per_step": own_e2e_ms / args.steps},
+            "slot_per_query_and_owner": own_slot, "slot_overflowed": own_overflow != 0.0,
+            "results_identical_to_peer_reads": own_bad == 0.0}),
         "ids_identical": ids_identical, "ids_checked_queries": checked,
         "ids_check": "sample of every rank's queries against the whole index searched unsharded on rank 0"
                      if ids_identical is not None else "skipped: the whole index does not fit one GPU beside the shards",

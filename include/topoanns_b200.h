@@ -334,6 +334,29 @@ TannStatus tann_topk_pack(const float* dists /*dev [Q][top_n]*/, const uint32_t*
                           uint32_t top_n, uint32_t top_k, float* out_dists /*dev [Q][top_k]*/,
                           uint32_t* out_ids, tann_stream_t stream);
 
+/* ---- exact rerank by the owner of the rows (indexes sharded by node-id range over several GPUs) ----
+ * NO COUNTERPART IN THE REFERENCE (single GPU). Instead of reading candidates' vectors from other GPUs'
+ * shards, the GPU that ran the traversal splits every query's candidate list by owner, the lists are
+ * exchanged (one all-to-all), every owner scores what it received against its own shard with
+ * tann_rerank_exact + tann_topk_pack on a view of that shard alone, the [Q][top_k] lists travel back (a
+ * second all-to-all) and are merged. Exact distances and the (distance, id) order do not depend on where a
+ * row is scored: the result is the unsharded one, bit for bit.
+ *
+ * tann_partition_candidates: ranks [0, min(top_n, capacity)) of every list; owner = id / rows_per_shard.
+ *   out       dev [num_owners][Q][slot] records (id = row number inside the owner's shard, distance kept);
+ *             unused tail = (0xffffffff, 0); ids beyond the last owner are dropped;
+ *   overflow  dev uint32, or-ed with 1 when some (query, owner) list had more than `slot` records (the
+ *             excess is dropped: rerun with a larger slot; slot = top_n can never overflow).
+ * tann_merge_topk_lists: dists / ids dev [num_lists][Q][top_k] sorted lists (top_k <= 32), list l holding
+ *   row numbers of shard l; out dev [Q][top_k]: the top_k smallest by (distance, l * rows_per_shard + id),
+ *   ids global; unfilled = (+inf, 0xffffffff). */
+TannStatus tann_partition_candidates(const void* candidates /*dev [Q][capacity]*/, uint32_t capacity, uint32_t top_n,
+                                     uint64_t num_queries, uint64_t rows_per_shard, uint32_t num_owners,
+                                     uint32_t slot, void* out, uint32_t* overflow, tann_stream_t stream);
+TannStatus tann_merge_topk_lists(const float* dists, const uint32_t* ids, uint32_t num_lists, uint64_t num_queries,
+                                 uint32_t top_k, uint64_t rows_per_shard, float* out_dists, uint32_t* out_ids,
+                                 tann_stream_t stream);
+
 /* Exact rerank + top-k of one batch (tann_rerank_exact followed by tann_topk_pack, same results)
  * that allocates nothing: its work space is a fixed device array of TANN_STATIC_SCRATCH_BYTES inside
  * the library. NO COUNTERPART IN THE REFERENCE. It is for callers that may not call cudaMalloc /

@@ -392,6 +392,64 @@ def test_rerank_short_tiles_match_checker(tile, top_k, top_n, float_queries):
     assert np.array_equal(d.cpu().numpy().view(np.uint32), rd.view(np.uint32))
 
 
+@pytest.mark.parametrize("owners,float_queries", [(4, False), (3, True), (7, False)])
+def test_rerank_by_owner_matches_plain_rerank(owners, float_queries):
+    """Candidate lists split by the owner of the rows, every owner's list scored against its slice of the vector
+    pages alone, the per-owner top-k lists merged: ids and distance bits of the plain rerank of the whole list."""
+    import ctypes as C
+    import dataclasses
+    s, host = small_index()
+    ix = device_index(s)
+    lib = capi.load()
+    Q, N = s.queries.shape[0], ix.num_nodes
+    top_n, k = 200, 10
+    eo, ei = fixed_entries(Q, [s.medoid])
+    p = search.TopologySearchParams(top_l=top_n, search_width=2, max_expansions=4096)
+    q8 = s.queries.cuda().to(torch.uint8).contiguous()
+    cand, _ = search.beam_search(ix, p, eo, ei, queries=q8, capacity=p.capacity(top_n))
+    q = (s.queries.cuda().float().contiguous() + 0.5) if float_queries else q8
+    rp = search.RerankExactParams(top_k=k, top_n=top_n)
+    d, i, _, _ = search.rerank_exact(ix, rp, cand, q)
+    want_d, want_i = search.topk_pack(d, i, k)
+    vpp = ix.vectors_per_page
+    rows = ((N + owners - 1) // owners + vpp - 1) // vpp * vpp
+    ptr = lambda t: C.c_void_p(t.data_ptr())
+    for slot in (top_n, 8):
+        parts = torch.empty((owners, Q, slot, 2), dtype=torch.int32, device="cuda")
+        overflow = torch.zeros(1, dtype=torch.int32, device="cuda")
+        capi.check(lib.tann_partition_candidates(ptr(cand), cand.shape[1], top_n, Q, rows, owners, slot, ptr(parts),
+                                                 ptr(overflow), None))
+        if slot < top_n:
+            assert int(overflow.item()) == 1      # the mixture's candidates crowd into few owners
+            continue
+        assert int(overflow.item()) == 0
+        raw = parts.cpu().numpy().view(np.uint32)          # records are (distance bits, id)
+        all_ids = np_u32(cand)[:, :top_n, 1]
+        for o in range(owners):                   # every candidate sits in its owner's list, in rank order
+            for qi in (0, Q // 2, Q - 1):
+                valid = all_ids[qi] != 0xffffffff
+                rid = all_ids[qi] & 0x7fffffff
+                pick = valid & (rid // rows == o)
+                assert np.array_equal(raw[o, qi, :pick.sum(), 1], rid[pick] - o * rows)
+                assert np.array_equal(raw[o, qi, :pick.sum(), 0], np_u32(cand)[qi, :top_n, 0][pick])
+                assert (raw[o, qi, pick.sum():, 1] == 0xffffffff).all()
+        lists_d = torch.empty((owners, Q, k), dtype=torch.float32, device="cuda")
+        lists_i = torch.empty((owners, Q, k), dtype=torch.int32, device="cuda")
+        for o in range(owners):
+            n_o = min(rows, N - o * rows)
+            first_page = o * rows // vpp
+            local = dataclasses.replace(ix, num_nodes=n_o,
+                                        vector_pages=ix.vector_pages[first_page * ix.page_bytes:])
+            od, oi, _, _ = search.rerank_exact(local, search.RerankExactParams(top_k=k, top_n=slot), parts[o], q)
+            pd, pi = search.topk_pack(od, oi, k)
+            lists_d[o], lists_i[o] = pd, pi
+        out_d = torch.empty((Q, k), dtype=torch.float32, device="cuda")
+        out_i = torch.empty((Q, k), dtype=torch.int32, device="cuda")
+        capi.check(lib.tann_merge_topk_lists(ptr(lists_d), ptr(lists_i), owners, Q, k, rows, ptr(out_d), ptr(out_i), None))
+        assert torch.equal(out_i, want_i)
+        assert np.array_equal(out_d.cpu().numpy().view(np.uint32), want_d.cpu().numpy().view(np.uint32))
+
+
 def test_rerank_int8_vectors():
     """Stored int8 vectors (the third scalar kind of the vector store) with int8 and float queries."""
     s, host = small_index()

@@ -119,6 +119,8 @@ SIGNATURES = {
                                             C.POINTER(RerankLearnedStop), _VP, _U32, _U64, _VP, _U32, _VP, _VP,
                                             _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP]),
     "tann_topk_pack": (_I, [_VP, _VP, _U64, _U32, _U32, _VP, _VP, _VP]),
+    "tann_partition_candidates": (_I, [_VP, _U32, _U32, _U64, _U64, _U32, _U32, _VP, _VP, _VP]),
+    "tann_merge_topk_lists": (_I, [_VP, _VP, _U32, _U64, _U32, _U64, _VP, _VP, _VP]),
     "tann_rerank_topk_static": (_I, [C.POINTER(IndexView), C.POINTER(RerankParams), _VP, _U32, _U64, _VP, _U32,
                                      _VP, _VP, _VP, _VP]),
     "tann_neighbor_codes_build": (_I, [C.POINTER(IndexView), _U64, _U64, _VP, _VP]),

@@ -145,3 +145,78 @@ def peer_index_from_sharded(sh):
         keepalive=[buffers])
     _ = dev
     return ix, buffers
+
+
+class OwnerRerank:
+    """Exact rerank by the owner of the rows, for an index sharded by node-id range (one process per GPU).
+
+    Reading candidates' vectors from the peers' shards is one random access into another GPU's memory per
+    candidate; over shards of tens of GB those accesses spread over hundreds of GB of peer address space and
+    their rate collapses. Here the candidates travel instead: every rank splits its queries' candidate lists by
+    owner (`tann_partition_candidates`), one all-to-all hands every owner its lists, the owner scores them against
+    its own shard (`tann_rerank_exact` + `tann_topk_pack` on a view of that shard alone), a second all-to-all
+    returns the [Q, k] lists and `tann_merge_topk_lists` merges them by (distance, global id). The result is the
+    unsharded one bit for bit. Every rank must call `run` with the same number of queries.
+
+    `local_index` is a `search.DeviceIndex` over this rank's shard only (num_nodes = rows_per_shard, one base per
+    array). `slot` is the room per (query, owner) list; 0 picks twice the even share plus 32, at most top_n. A list
+    that outgrows its slot sets a flag that `overflowed()` reads back (the results of that call are then short of
+    some candidates: build a new object with slot = top_n, which cannot overflow)."""
+
+    def __init__(self, local_index, rows_per_shard: int, max_queries: int, top_n: int, top_k: int,
+                 query_dtype: torch.dtype, slot: int = 0, group=None):
+        from . import search
+        self._search = search
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rows = int(rows_per_shard)
+        self.top_n, self.top_k = int(top_n), int(top_k)
+        if slot <= 0:
+            slot = 2 * ((top_n + self.world - 1) // self.world) + 32
+        self.slot = max(self.top_k, min(int(slot), self.top_n))
+        self.local_index = local_index
+        self._view = local_index.view()
+        W, Q, dev = self.world, int(max_queries), local_index.pq_centroid.device
+        self.max_queries = Q
+        self.send = torch.empty((W, Q, self.slot, 2), dtype=torch.int32, device=dev)
+        self.recv = torch.empty_like(self.send)
+        self.all_q = torch.empty((W, Q, local_index.dim), dtype=query_dtype, device=dev)
+        self.dists = torch.empty((W * Q, self.slot), dtype=torch.float32, device=dev)
+        self.ids = torch.empty((W * Q, self.slot), dtype=torch.int32, device=dev)
+        self.pack_d = torch.empty((W, Q, self.top_k), dtype=torch.float32, device=dev)
+        self.pack_i = torch.empty((W, Q, self.top_k), dtype=torch.int32, device=dev)
+        self.back_d = torch.empty_like(self.pack_d)
+        self.back_i = torch.empty_like(self.pack_i)
+        self.out_d = torch.empty((Q, self.top_k), dtype=torch.float32, device=dev)
+        self.out_i = torch.empty((Q, self.top_k), dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._params = capi.RerankParams(self.slot, self.top_k, 0, 0, 0, 0, 0, 0)
+
+    def run(self, cand: torch.Tensor, queries: torch.Tensor):
+        """cand: [Q, capacity, 2] candidate records of this rank's queries (global ids); queries: [Q, dim].
+        Returns (ids [Q, top_k] int32 holding global ids, dists [Q, top_k]) - buffers reused by the next call."""
+        lib = capi.load()
+        Q, capacity = int(cand.shape[0]), int(cand.shape[1])
+        if Q != self.max_queries:
+            raise ValueError("OwnerRerank.run: every call takes max_queries queries on every rank")
+        W, st = self.world, C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        p = lambda t: C.c_void_p(t.data_ptr())
+        capi.check(lib.tann_partition_candidates(p(cand), capacity, self.top_n, Q, self.rows, W, self.slot,
+                                                 p(self.send), p(self.overflow), st))
+        dist.all_to_all_single(self.recv, self.send, group=self.group)      # recv[h]: rank h's queries, my rows
+        dist.all_gather_into_tensor(self.all_q, queries.contiguous(), group=self.group)
+        capi.check(lib.tann_rerank_exact(C.byref(self._view), C.byref(self._params), p(self.recv), self.slot, W * Q,
+                                         p(self.all_q), self._search.kind_of(self.all_q), None, p(self.dists),
+                                         p(self.ids), None, None, st))
+        capi.check(lib.tann_topk_pack(p(self.dists), p(self.ids), W * Q, self.slot, self.top_k, p(self.pack_d),
+                                      p(self.pack_i), st))
+        dist.all_to_all_single(self.back_d, self.pack_d, group=self.group)  # back[o]: my queries, owner o's rows
+        dist.all_to_all_single(self.back_i, self.pack_i, group=self.group)
+        capi.check(lib.tann_merge_topk_lists(p(self.back_d), p(self.back_i), W, Q, self.top_k, self.rows,
+                                             p(self.out_d), p(self.out_i), st))
+        return self.out_i, self.out_d
+
+    def overflowed(self) -> bool:
+        """True if some (query, owner) list outgrew its slot since the object was built (synchronises)."""
+        return bool(int(self.overflow.item()) != 0)
