@@ -112,3 +112,116 @@ def test_node_range_sharded_generator(tmp_path):
     out = tmp_path / "result.txt"
     mp.spawn(_sharded_worker, args=(2, port, str(out)), nprocs=2, join=True)
     assert out.read_text() == "ok"
+
+
+class _TorchOwnerOps:
+    """Plain torch stand-ins for the three device steps of sharding.OwnerRerank (same contracts as the C ABI's
+    tann_partition_candidates, tann_rerank_exact + tann_topk_pack, tann_merge_topk_lists), for CPU ranks."""
+
+    def __init__(self, local_vectors):
+        self.vectors = local_vectors.to(torch.int64)          # [rows, dim]
+        self.device = torch.device("cpu")
+        self.dim = local_vectors.shape[1]
+
+    def partition(self, cand, top_n, rows, owners, slot, out, overflow):
+        out[..., 0] = 0
+        out[..., 1] = -1
+        n = min(top_n, cand.shape[1])
+        for q in range(cand.shape[0]):
+            used = [0] * owners
+            for r in range(n):
+                bits, raw = int(cand[q, r, 0]), int(cand[q, r, 1]) & 0xffffffff
+                if raw == 0xffffffff:
+                    continue
+                raw &= 0x7fffffff
+                o = raw // rows
+                if o >= owners:
+                    continue
+                if used[o] < slot:
+                    out[o, q, used[o], 0] = bits
+                    out[o, q, used[o], 1] = raw - o * rows
+                    used[o] += 1
+                else:
+                    overflow[0] = 1
+
+    def rerank_topk(self, lists, queries, slot, top_k, dists, ids, out_d, out_i):
+        flat = lists.reshape(-1, slot, 2)
+        qs = queries.reshape(-1, self.dim).to(torch.int64)
+        for n in range(flat.shape[0]):
+            keys = []
+            for j in range(slot):
+                row = int(flat[n, j, 1])
+                if row < 0 or row >= self.vectors.shape[0]:
+                    continue
+                d = int(((self.vectors[row] - qs[n]) ** 2).sum())
+                keys.append((float(d), row))
+            keys.sort()
+            keys = (keys + [(float("inf"), -1)] * top_k)[:top_k]
+            out_d.view(-1, top_k)[n] = torch.tensor([k[0] for k in keys])
+            out_i.view(-1, top_k)[n] = torch.tensor([k[1] for k in keys], dtype=torch.int32)
+
+    def merge(self, lists_d, lists_i, rows, out_d, out_i):
+        W, Q, k = lists_d.shape
+        for q in range(Q):
+            keys = []
+            for l in range(W):
+                for j in range(k):
+                    if int(lists_i[l, q, j]) >= 0:
+                        keys.append((float(lists_d[l, q, j]), int(lists_i[l, q, j]) + l * rows))
+            keys.sort()
+            keys = (keys + [(float("inf"), -1)] * k)[:k]
+            out_d[q] = torch.tensor([x[0] for x in keys])
+            out_i[q] = torch.tensor([x[1] for x in keys], dtype=torch.int32)
+
+
+def _owner_worker(rank, world, port, out_path):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    g = torch.Generator().manual_seed(99)                       # the same data on every rank
+    rows, dim, Q, cap, top_n, k = 96, 16, 9, 64, 40, 5
+    vectors = torch.randint(0, 256, (rows * world, dim), generator=g, dtype=torch.int64).to(torch.uint8)
+    queries = torch.randint(0, 256, (world, Q, dim), generator=g, dtype=torch.int64).to(torch.uint8)
+    ids = torch.stack([torch.stack([torch.randperm(rows * world, generator=g)[:cap] for _ in range(Q)])
+                       for _ in range(world)]).to(torch.int32)
+    ids[:, :, 7] = -1                                            # an empty rank in every list
+    ids[:, 0, 3] |= -0x80000000                                  # the traversal's "expanded" bit on one record
+    cand = torch.stack([torch.zeros_like(ids), ids], dim=3)      # (distance bits, id); the distance is not used here
+    ok = True
+    for slot in (0, top_n):
+        orr = sharding.OwnerRerank(None, rows, Q, top_n, k, torch.uint8, slot=slot,
+                                   ops=_TorchOwnerOps(vectors[rank * rows:(rank + 1) * rows]))
+        got_i, got_d = orr.run(cand[rank], queries[rank])
+        # the unsharded answer: exact distances of the first top_n ranks against the whole matrix, by (distance, id)
+        for q in range(Q):
+            keys = []
+            for r in range(top_n):
+                raw = int(ids[rank, q, r])
+                if raw == -1:
+                    continue
+                raw &= 0x7fffffff
+                d = int(((vectors[raw].to(torch.int64) - queries[rank, q].to(torch.int64)) ** 2).sum())
+                keys.append((float(d), raw))
+            keys.sort()
+            want = keys[:k]
+            ok = ok and [int(x) for x in got_i[q]] == [w[1] for w in want] and \
+                [float(x) for x in got_d[q]] == [w[0] for w in want]
+        ok = ok and not orr.overflowed()
+    flag = torch.tensor([1 if ok else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        open(out_path, "w").write("ok" if int(flag) == 1 else "mismatch")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_rerank_by_owner_exchange_on_three_ranks(tmp_path):
+    """The two all-to-alls and the query all-gather of sharding.OwnerRerank, with the device steps replaced by plain
+    torch code: every rank ends up with the top-k of its own queries over the rows of all ranks."""
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    out = tmp_path / "owner.txt"
+    mp.spawn(_owner_worker, args=(3, port, str(out)), nprocs=3, join=True)
+    assert out.read_text() == "ok"

@@ -147,6 +147,43 @@ def peer_index_from_sharded(sh):
     return ix, buffers
 
 
+class _CudaOwnerOps:
+    """The three device steps of OwnerRerank through the C ABI, on the current CUDA stream."""
+
+    def __init__(self, local_index):
+        from . import search
+        self._kind_of = search.kind_of
+        self._view = local_index.view()
+        self.device = local_index.pq_centroid.device
+        self.dim = local_index.dim
+
+    @staticmethod
+    def _p(t):
+        return C.c_void_p(t.data_ptr())
+
+    @staticmethod
+    def _stream():
+        return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def partition(self, cand, top_n, rows, owners, slot, out, overflow):
+        capi.check(capi.load().tann_partition_candidates(self._p(cand), int(cand.shape[1]), top_n, int(cand.shape[0]), rows,
+                                                         owners, slot, self._p(out), self._p(overflow), self._stream()))
+
+    def rerank_topk(self, lists, queries, slot, top_k, dists, ids, out_d, out_i):
+        lib, n = capi.load(), int(queries.shape[0]) * int(queries.shape[1])
+        params = capi.RerankParams(slot, top_k, 0, 0, 0, 0, 0, 0)
+        capi.check(lib.tann_rerank_exact(C.byref(self._view), C.byref(params), self._p(lists), slot, n, self._p(queries),
+                                         self._kind_of(queries), None, self._p(dists), self._p(ids), None, None,
+                                         self._stream()))
+        capi.check(lib.tann_topk_pack(self._p(dists), self._p(ids), n, slot, top_k, self._p(out_d), self._p(out_i),
+                                      self._stream()))
+
+    def merge(self, lists_d, lists_i, rows, out_d, out_i):
+        W, Q, k = (int(x) for x in lists_d.shape)
+        capi.check(capi.load().tann_merge_topk_lists(self._p(lists_d), self._p(lists_i), W, Q, k, rows, self._p(out_d),
+                                                     self._p(out_i), self._stream()))
+
+
 class OwnerRerank:
     """Exact rerank by the owner of the rows, for an index sharded by node-id range (one process per GPU).
 
@@ -161,12 +198,11 @@ class OwnerRerank:
     `local_index` is a `search.DeviceIndex` over this rank's shard only (num_nodes = rows_per_shard, one base per
     array). `slot` is the room per (query, owner) list; 0 picks twice the even share plus 32, at most top_n. A list
     that outgrows its slot sets a flag that `overflowed()` reads back (the results of that call are then short of
-    some candidates: build a new object with slot = top_n, which cannot overflow)."""
+    some candidates: build a new object with slot = top_n, which cannot overflow). `ops` replaces the three device
+    steps (the CPU tests of the exchange pass plain torch code); by default they are the library's kernels."""
 
     def __init__(self, local_index, rows_per_shard: int, max_queries: int, top_n: int, top_k: int,
-                 query_dtype: torch.dtype, slot: int = 0, group=None):
-        from . import search
-        self._search = search
+                 query_dtype: torch.dtype, slot: int = 0, group=None, ops=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -175,13 +211,12 @@ class OwnerRerank:
         if slot <= 0:
             slot = 2 * ((top_n + self.world - 1) // self.world) + 32
         self.slot = max(self.top_k, min(int(slot), self.top_n))
-        self.local_index = local_index
-        self._view = local_index.view()
-        W, Q, dev = self.world, int(max_queries), local_index.pq_centroid.device
+        self.ops = ops if ops is not None else _CudaOwnerOps(local_index)
+        W, Q, dev = self.world, int(max_queries), self.ops.device
         self.max_queries = Q
         self.send = torch.empty((W, Q, self.slot, 2), dtype=torch.int32, device=dev)
         self.recv = torch.empty_like(self.send)
-        self.all_q = torch.empty((W, Q, local_index.dim), dtype=query_dtype, device=dev)
+        self.all_q = torch.empty((W, Q, self.ops.dim), dtype=query_dtype, device=dev)
         self.dists = torch.empty((W * Q, self.slot), dtype=torch.float32, device=dev)
         self.ids = torch.empty((W * Q, self.slot), dtype=torch.int32, device=dev)
         self.pack_d = torch.empty((W, Q, self.top_k), dtype=torch.float32, device=dev)
@@ -191,30 +226,20 @@ class OwnerRerank:
         self.out_d = torch.empty((Q, self.top_k), dtype=torch.float32, device=dev)
         self.out_i = torch.empty((Q, self.top_k), dtype=torch.int32, device=dev)
         self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._params = capi.RerankParams(self.slot, self.top_k, 0, 0, 0, 0, 0, 0)
 
     def run(self, cand: torch.Tensor, queries: torch.Tensor):
-        """cand: [Q, capacity, 2] candidate records of this rank's queries (global ids); queries: [Q, dim].
-        Returns (ids [Q, top_k] int32 holding global ids, dists [Q, top_k]) - buffers reused by the next call."""
-        lib = capi.load()
-        Q, capacity = int(cand.shape[0]), int(cand.shape[1])
-        if Q != self.max_queries:
+        """cand: [Q, capacity, 2] candidate records (distance bits, id) of this rank's queries, ids global;
+        queries: [Q, dim]. Returns (ids [Q, top_k] int32 holding global ids, dists [Q, top_k]) - buffers that the
+        next call reuses."""
+        if int(cand.shape[0]) != self.max_queries:
             raise ValueError("OwnerRerank.run: every call takes max_queries queries on every rank")
-        W, st = self.world, C.c_void_p(torch.cuda.current_stream().cuda_stream)
-        p = lambda t: C.c_void_p(t.data_ptr())
-        capi.check(lib.tann_partition_candidates(p(cand), capacity, self.top_n, Q, self.rows, W, self.slot,
-                                                 p(self.send), p(self.overflow), st))
+        self.ops.partition(cand, self.top_n, self.rows, self.world, self.slot, self.send, self.overflow)
         dist.all_to_all_single(self.recv, self.send, group=self.group)      # recv[h]: rank h's queries, my rows
-        dist.all_gather_into_tensor(self.all_q, queries.contiguous(), group=self.group)
-        capi.check(lib.tann_rerank_exact(C.byref(self._view), C.byref(self._params), p(self.recv), self.slot, W * Q,
-                                         p(self.all_q), self._search.kind_of(self.all_q), None, p(self.dists),
-                                         p(self.ids), None, None, st))
-        capi.check(lib.tann_topk_pack(p(self.dists), p(self.ids), W * Q, self.slot, self.top_k, p(self.pack_d),
-                                      p(self.pack_i), st))
+        dist.all_gather_into_tensor(self.all_q.view(-1, self.all_q.shape[2]), queries.contiguous(), group=self.group)
+        self.ops.rerank_topk(self.recv, self.all_q, self.slot, self.top_k, self.dists, self.ids, self.pack_d, self.pack_i)
         dist.all_to_all_single(self.back_d, self.pack_d, group=self.group)  # back[o]: my queries, owner o's rows
         dist.all_to_all_single(self.back_i, self.pack_i, group=self.group)
-        capi.check(lib.tann_merge_topk_lists(p(self.back_d), p(self.back_i), W, Q, self.top_k, self.rows,
-                                             p(self.out_d), p(self.out_i), st))
+        self.ops.merge(self.back_d, self.back_i, self.rows, self.out_d, self.out_i)
         return self.out_i, self.out_d
 
     def overflowed(self) -> bool:
