@@ -60,11 +60,14 @@ __device__ __forceinline__ void OctetRanksInt(unsigned long long* keys, const ui
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         uint32_t acc[kStep];
+        bool live = false;
 #pragma unroll
         for (uint32_t g = 0; g < kStep; ++g) {
             ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
             acc[g] = 0;
+            live = live || ptr[g] != kInvalidKey64;
         }
+        if (!__any_sync(kFull, live)) continue;   // every slot of this step is empty (filtered or past the list)
         for (uint32_t j = ol; j < pieces; j += 8) {
             uint4 v[kStep];
 #pragma unroll
@@ -105,11 +108,14 @@ __device__ __forceinline__ void OctetRanksF32(unsigned long long* keys, const ui
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         float acc[kStep][4];
+        bool live = false;
 #pragma unroll
         for (uint32_t g = 0; g < kStep; ++g) {
             ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
             acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+            live = live || ptr[g] != kInvalidKey64;
         }
+        if (!__any_sync(kFull, live)) continue;   // every slot of this step is empty (filtered or past the list)
         for (uint32_t d0 = 4 * ol; d0 < dim; d0 += 32) {
             float4 v[kStep];
 #pragma unroll
@@ -155,11 +161,14 @@ __device__ __forceinline__ void OctetRanksU8F32(unsigned long long* keys, const 
         const uint32_t r0 = w0 + (octet & 3u) * kStep;
         unsigned long long ptr[kStep];
         float acc[kStep][4];
+        bool live = false;
 #pragma unroll
         for (uint32_t g = 0; g < kStep; ++g) {
             ptr[g] = (r0 + g < end) ? keys[r0 + g] : kInvalidKey64;
             acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.0f;
+            live = live || ptr[g] != kInvalidKey64;
         }
+        if (!__any_sync(kFull, live)) continue;   // every slot of this step is empty (filtered or past the list)
         for (uint32_t d0 = 4 * ol; d0 < dim; d0 += 32) {
             uint32_t v[kStep];
 #pragma unroll
@@ -235,6 +244,10 @@ __device__ __forceinline__ void ScoreRanks(const TannIndexView& ix, const ScoreM
                 act[g] = slot != kInvalidKey64;
                 vptr[g] = reinterpret_cast<const uint8_t*>(slot);
             }
+            bool live = false;
+#pragma unroll
+            for (uint32_t g = 0; g < kGroup; ++g) live = live || act[g];
+            if (!live) continue;   // the same for every lane of the warp
             float dist[kGroup];
             if (int_path) {
                 uint32_t acc[kGroup];
