@@ -607,10 +607,8 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                     __syncthreads();
                 }
             }
-            if (kSingle) {
-                __syncthreads();  // every test of the round precedes every add
-                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane, mark_pos);
-            }
+            // kSingle: the adds of this round and the expanded marks wait for the compaction barrier below, which
+            // every test of the round precedes as well
             TANN_PHASE(2);  // 2: slot ids (adjacency / entries) + Bloom tests
             // ---- phase 2: Bloom adds, code gathers, ADC sums ------------------------------------
             uint32_t fv = 0;
@@ -620,7 +618,6 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 const bool pass = parked != kInvalidKey;
                 if (pass) {
                     const uint32_t id = (uint32_t)parked;
-                    if (kSingle) BloomAdd(my_bits, bloom);
                     float dist;
                     if constexpr (kSingle && kM > 0) {
                         dist = AdcFromWords<kM>(lut, my_words);
@@ -660,6 +657,8 @@ beam_search_kernel(const __grid_constant__ BeamArgs a) {
                 base = __shfl_sync(kFull, base, 0);
                 if (surv) fkey[base + __popc(ballot & ((1u << lane) - 1u))] = my_key;
                 __syncthreads();
+                if (pass) BloomAdd(my_bits, bloom);
+                if (tid < 32) MarkExpanded(cur, sel_word, sel_begin, sel_end, lane, mark_pos);
                 TANN_PHASE(8);  // 8: filter + compaction (waits for every code row)
                 const uint32_t n = s_surv;
                 fv = s_pass;
