@@ -83,6 +83,23 @@ def test_misaligned_tables_and_code_rows_are_rejected_before_any_launch():
     assert b"neighbor_codes shard 0 must be 16-byte aligned" in lib.tann_last_error()
 
 
+def test_owner_rerank_entry_points_reject_bad_sizes_before_any_launch():
+    """Owner counts, slots and shard sizes of the rerank-by-owner helpers are checked on the host."""
+    lib = capi.load()
+    x = 4096
+    assert lib.tann_partition_candidates(x, 64, 32, 10, 0, 8, 16, x, x, None) == 1          # rows_per_shard = 0
+    assert b"tann_partition_candidates" in lib.tann_last_error()
+    assert lib.tann_partition_candidates(x, 64, 32, 10, 1000, 65, 16, x, x, None) == 1      # more than 64 owners
+    assert lib.tann_partition_candidates(x, 64, 32, 10, 1000, 8, 0, x, x, None) == 1        # empty slot
+    assert lib.tann_partition_candidates(x, 64, 32, 10, 1000, 8, 16, x, None, None) == 1    # no overflow word
+    assert lib.tann_merge_topk_lists(x, x, 8, 10, 40, 1000, x, x, None) == 1                # top_k above 32
+    assert b"tann_merge_topk_lists" in lib.tann_last_error()
+    assert lib.tann_merge_topk_lists(x, x, 8, 10, 10, 1 << 30, x, x, None) == 1             # ids beyond 31 bits
+    assert lib.tann_merge_topk_lists(x, x, 0, 10, 10, 1000, x, x, None) == 1                # no list
+    assert lib.tann_partition_candidates(x, 64, 32, 0, 1000, 8, 16, x, x, None) == 0        # empty batch: no-op
+    assert lib.tann_merge_topk_lists(x, x, 8, 0, 10, 1000, x, x, None) == 0
+
+
 def test_capacity_rule():
     # nextpow2(max(top_l, candidate_queue_size, rerank top_n))
     assert capi.candidate_capacity(4, 0, 5) == 8

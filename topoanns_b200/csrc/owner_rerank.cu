@@ -168,9 +168,11 @@ TannStatus tann_merge_topk_lists(const float* dists, const uint32_t* ids, uint32
     if (num_queries == 0 || top_k == 0) return TANN_OK;
     if (!dists || !ids || !out_dists || !out_ids)
         return tann::OwnerFail(TANN_ERR_INVALID_ARGUMENT, "tann_merge_topk_lists: null pointer.");
-    if (num_lists == 0 || top_k > 32 || rows_per_shard > 0x7fffffffull)
+    if (num_lists == 0 || top_k > 32 || rows_per_shard > 0x7fffffffull ||
+        (uint64_t)num_lists * rows_per_shard > 0x80000000ull)
         return tann::OwnerFail(TANN_ERR_INVALID_ARGUMENT,
-                               "tann_merge_topk_lists: at least one list, top_k at most 32, rows_per_shard below 2^31.");
+                               "tann_merge_topk_lists: at least one list, top_k at most 32, num_lists * rows_per_shard "
+                               "at most 2^31 (node ids have 31 bits).");
     cudaError_t e = tann::LaunchMergeTopkLists(dists, ids, num_lists, num_queries, top_k, (uint32_t)rows_per_shard,
                                                out_dists, out_ids, (cudaStream_t)stream);
     if (e != cudaSuccess) return tann::OwnerFail(TANN_ERR_CUDA, cudaGetErrorString(e));
